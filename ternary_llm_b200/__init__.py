@@ -1,0 +1,13 @@
+"""ternary_llm_b200: B200-native ternary weight contraction (decode GEMV, prefill
+GEMM) behind the operator interface of jastaq/ternary-llm.
+
+The compute lives in libtllm_b200.so (hand-written sm_100a CUDA behind the C ABI
+of include/tllm_b200.h); this package is the thin host side.
+"""
+from . import pack  # noqa: F401
+from ._lib import LIB_PATH, TllmError, lib  # noqa: F401
+from .ops import (GROUP_SIZE, MAX_BATCH, quantize_absmax_int8, ternary_gemm,  # noqa: F401
+                  ternary_gemv, ternary_gemv_batched, ternary_gemv_int8)
+
+__all__ = ["pack", "lib", "TllmError", "LIB_PATH", "GROUP_SIZE", "MAX_BATCH", "ternary_gemv",
+           "ternary_gemv_batched", "ternary_gemv_int8", "quantize_absmax_int8", "ternary_gemm"]

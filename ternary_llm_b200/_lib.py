@@ -1,0 +1,58 @@
+"""ctypes binding of libtllm_b200.so (the C ABI in include/tllm_b200.h).
+
+There is no fallback: if the shared library is missing or a call fails, an
+exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libtllm_b200.so")
+
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+
+# name -> (restype, argtypes); must list every symbol include/tllm_b200.h declares
+SIGNATURES = {
+    "tllm_b200_status_string": (ctypes.c_char_p, [_int]),
+    "tllm_b200_last_error": (ctypes.c_char_p, []),
+    "tllm_b200_version": (_int, []),
+    "tllm_b200_gemv": (_int, [_vp] * 5 + [_int] * 3 + [_vp]),
+    "tllm_b200_gemv_batched": (_int, [_vp] * 5 + [_int] * 4 + [_vp]),
+    "tllm_b200_gemv_int8": (_int, [_vp] * 4 + [ctypes.c_float, _vp] + [_int] * 3 + [_vp]),
+    "tllm_b200_quantize_absmax_int8": (_int, [_vp] * 3 + [_int, _vp]),
+    "tllm_b200_gemm": (_int, [_vp] * 5 + [_int] * 4 + [_vp]),
+}
+
+
+class TllmError(RuntimeError):
+    def __init__(self, status: int, text: str, detail: str):
+        super().__init__(f"tllm_b200 status {status} ({text}): {detail}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m ternary_llm_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        h = lib()
+        raise TllmError(status, h.tllm_b200_status_string(status).decode(),
+                        h.tllm_b200_last_error().decode())

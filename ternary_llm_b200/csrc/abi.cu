@@ -1,0 +1,154 @@
+// extern "C" entry points of libtllm_b200: argument checks and dispatch.
+// Declarations, argument meaning and the reference interface each entry point
+// replaces are in include/tllm_b200.h.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace tllm {
+
+static thread_local char g_err[512] = "";
+
+int fail(int status, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int check_launch(const char* what)
+{
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();   // clear a non-sticky launch error so later calls can proceed
+        return fail(TLLM_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return TLLM_OK;
+}
+
+// The kernels are built for sm_100a only; refuse any other device loudly.
+static int check_device()
+{
+    static int ok[64] = {};   // 0 unknown, 1 good, -1 bad
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0)
+        return fail(TLLM_ERR_DEVICE, "no current CUDA device");
+    if (dev < 64 && ok[dev] == 1) return TLLM_OK;
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (dev < 64) ok[dev] = (major == 10) ? 1 : -1;
+    if (major != 10)
+        return fail(TLLM_ERR_DEVICE, "device %d has compute capability %d.x; this library is sm_100a only", dev, major);
+    return TLLM_OK;
+}
+
+static inline bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
+
+static int check_weights(const void* nz, const void* sg, const void* scales, int rows, int cols, int gs)
+{
+    if (!nz || !sg || !scales) return fail(TLLM_ERR_NULL, "null weight pointer");
+    if (gs != kGroup) return fail(TLLM_ERR_GROUP, "group_size %d unsupported (must be 128)", gs);
+    if (rows < 1 || cols < kGroup || cols % kGroup != 0)
+        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: need rows >= 1 and cols a positive multiple of 128", rows, cols);
+    if (misaligned(nz, 16) || misaligned(sg, 16)) return fail(TLLM_ERR_ALIGN, "mask pointers must be 16-byte aligned");
+    if (misaligned(scales, 2)) return fail(TLLM_ERR_ALIGN, "scale pointer must be 2-byte aligned");
+    return TLLM_OK;
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" {
+
+const char* tllm_b200_status_string(int status)
+{
+    switch (status) {
+        case TLLM_OK: return "ok";
+        case TLLM_ERR_NULL: return "null pointer";
+        case TLLM_ERR_ALIGN: return "misaligned pointer";
+        case TLLM_ERR_SHAPE: return "unsupported shape";
+        case TLLM_ERR_GROUP: return "unsupported group size";
+        case TLLM_ERR_BATCH: return "batch out of range";
+        case TLLM_ERR_LAUNCH: return "CUDA launch or runtime error";
+        case TLLM_ERR_DEVICE: return "not an sm_100 device";
+        case TLLM_ERR_NONCANON: return "sign bit set without nonzero bit";
+        case TLLM_ERR_SIZE: return "buffer too small or size over the stated maximum";
+        case TLLM_ERR_TIMEOUT: return "bounded device wait gave up";
+        default: return "unknown status";
+    }
+}
+
+const char* tllm_b200_last_error(void) { return g_err; }
+
+int tllm_b200_version(void) { return 1000; }
+
+int tllm_b200_gemv_batched(const uint32_t* nz, const uint32_t* sg, const void* scales,
+                           const void* x, void* y, int batch, int rows, int cols,
+                           int group_size, void* stream)
+{
+    int st = check_weights(nz, sg, scales, rows, cols, group_size);
+    if (st) return st;
+    if (!x || !y) return fail(TLLM_ERR_NULL, "null activation or output pointer");
+    if (batch < 1 || batch > kMaxBatch) return fail(TLLM_ERR_BATCH, "batch %d outside 1..%d", batch, kMaxBatch);
+    if (misaligned(x, 16)) return fail(TLLM_ERR_ALIGN, "activation pointer must be 16-byte aligned");
+    if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
+    if ((st = check_device())) return st;
+    return launch_gemv_simt(nz, sg, (const half*)scales, (const half*)x, (half*)y, batch, rows, cols,
+                            (cudaStream_t)stream);
+}
+
+int tllm_b200_gemv(const uint32_t* nz, const uint32_t* sg, const void* scales, const void* x,
+                   void* y, int rows, int cols, int group_size, void* stream)
+{
+    return tllm_b200_gemv_batched(nz, sg, scales, x, y, 1, rows, cols, group_size, stream);
+}
+
+int tllm_b200_gemv_int8(const uint32_t* nz, const uint32_t* sg, const void* weight_scales,
+                        const int8_t* input_int8, float input_scale, void* y,
+                        int rows, int cols, int group_size, void* stream)
+{
+    int st = check_weights(nz, sg, weight_scales, rows, cols, group_size);
+    if (st) return st;
+    if (!input_int8 || !y) return fail(TLLM_ERR_NULL, "null activation or output pointer");
+    if (misaligned(input_int8, 16)) return fail(TLLM_ERR_ALIGN, "int8 activation pointer must be 16-byte aligned");
+    if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
+    if ((st = check_device())) return st;
+    return launch_gemv_int8_simt(nz, sg, (const half*)weight_scales, input_int8, input_scale, (half*)y,
+                                 rows, cols, (cudaStream_t)stream);
+}
+
+int tllm_b200_quantize_absmax_int8(const void* x, int8_t* q, float* scale, int n, void* stream)
+{
+    if (!x || !q || !scale) return fail(TLLM_ERR_NULL, "null pointer");
+    if (n < 1) return fail(TLLM_ERR_SHAPE, "n=%d must be positive", n);
+    if (misaligned(x, 2) || misaligned(scale, 4)) return fail(TLLM_ERR_ALIGN, "misaligned input or scale pointer");
+    int st = check_device();
+    if (st) return st;
+    return launch_quantize_absmax_int8((const half*)x, q, scale, n, (cudaStream_t)stream);
+}
+
+int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B, const void* scales_B,
+                   void* C, int M, int N, int K, int group_size, void* stream)
+{
+    int st = check_weights(nz_B, sign_B, scales_B, N, K, group_size);
+    if (st) return st;
+    if (!A || !C) return fail(TLLM_ERR_NULL, "null A or C pointer");
+    if (M < 1) return fail(TLLM_ERR_SHAPE, "M=%d must be positive", M);
+    if (misaligned(A, 16)) return fail(TLLM_ERR_ALIGN, "A must be 16-byte aligned");
+    if (misaligned(C, 2)) return fail(TLLM_ERR_ALIGN, "C must be 2-byte aligned");
+    if ((st = check_device())) return st;
+    // Token blocks of at most kMaxBatch rows, each one pass over the weights.
+    for (int m0 = 0; m0 < M; m0 += kMaxBatch) {
+        const int b = (M - m0 < kMaxBatch) ? (M - m0) : kMaxBatch;
+        st = launch_gemv_simt(nz_B, sign_B, (const half*)scales_B, (const half*)A + (size_t)m0 * K,
+                              (half*)C + (size_t)m0 * N, b, N, K, (cudaStream_t)stream);
+        if (st) return st;
+    }
+    return TLLM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,45 @@
+// Shared declarations for the tllm_b200 CUDA sources (sm_100a only).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "tllm_b200.h"
+
+namespace tllm {
+
+constexpr int kGroup = TLLM_GROUP_SIZE;   // weights per scale group along K
+constexpr int kMaxBatch = TLLM_MAX_BATCH;
+
+// Records a message for tllm_b200_last_error() and returns `status`.
+int fail(int status, const char* fmt, ...);
+// cudaPeekAtLastError -> status (does not clear sticky errors, does not sync).
+int check_launch(const char* what);
+
+// ---- launchers implemented in the kernel translation units ----------------
+// General-shape SIMT kernels on the reference layout (any rows >= 1).
+int launch_gemv_simt(const uint32_t* nz, const uint32_t* sg, const half* scales,
+                     const half* x, half* y, int batch, int rows, int cols,
+                     cudaStream_t stream);
+int launch_gemv_int8_simt(const uint32_t* nz, const uint32_t* sg, const half* scales,
+                          const int8_t* xq, float input_scale, half* y, int rows, int cols,
+                          cudaStream_t stream);
+int launch_quantize_absmax_int8(const half* x, int8_t* q, float* scale, int n,
+                                cudaStream_t stream);
+
+// ---- small device helpers --------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace tllm

@@ -1,0 +1,86 @@
+"""Host-side mirror of the reference's operator interface for the contraction path.
+
+The four functions carry the names and argument order of the reference's
+include/kernels.cuh:11-40 (namespace ternary) and call the C ABI of
+libtllm_b200.so with the tensors' device pointers on torch's current stream.
+PyTorch is used only to own device memory and streams.  All tensors must be
+CUDA tensors on the current device and contiguous; nothing here computes on the
+CPU or falls back to torch ops.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+GROUP_SIZE = 128
+MAX_BATCH = 16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t: torch.Tensor, dtype, name: str) -> int:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _mask_dtype_ok(t: torch.Tensor) -> bool:
+    return t.dtype in (torch.int32, torch.uint32)
+
+
+def _weights(nonzero_masks, sign_masks, scales):
+    for n, t in (("nonzero_masks", nonzero_masks), ("sign_masks", sign_masks)):
+        if not _mask_dtype_ok(t):
+            raise TypeError(f"{n} must be int32/uint32 words, got {t.dtype}")
+    return (_chk(nonzero_masks, nonzero_masks.dtype, "nonzero_masks"),
+            _chk(sign_masks, sign_masks.dtype, "sign_masks"),
+            _chk(scales, torch.float16, "scales"))
+
+
+def ternary_gemv(nonzero_masks, sign_masks, scales, input, output, rows: int, cols: int,
+                 group_size: int = GROUP_SIZE) -> None:
+    """y = W x for one FP16 vector (reference include/kernels.cuh:11-14)."""
+    nz, sg, sc = _weights(nonzero_masks, sign_masks, scales)
+    _lib.check(_lib.lib().tllm_b200_gemv(nz, sg, sc, _chk(input, torch.float16, "input"),
+                                         _chk(output, torch.float16, "output"),
+                                         rows, cols, group_size, _stream()))
+
+
+def ternary_gemv_batched(nonzero_masks, sign_masks, scales, input, output, batch: int, rows: int,
+                         cols: int, group_size: int = GROUP_SIZE) -> None:
+    """y[b] = W x[b] for 1..16 vectors in one pass over the weights."""
+    nz, sg, sc = _weights(nonzero_masks, sign_masks, scales)
+    _lib.check(_lib.lib().tllm_b200_gemv_batched(nz, sg, sc, _chk(input, torch.float16, "input"),
+                                                 _chk(output, torch.float16, "output"),
+                                                 batch, rows, cols, group_size, _stream()))
+
+
+def ternary_gemv_int8(nonzero_masks, sign_masks, weight_scales, input_int8, input_scale: float,
+                      output, rows: int, cols: int, group_size: int = GROUP_SIZE) -> None:
+    """INT8-activation GEMV (reference include/kernels.cuh:19-24)."""
+    nz, sg, sc = _weights(nonzero_masks, sign_masks, weight_scales)
+    _lib.check(_lib.lib().tllm_b200_gemv_int8(nz, sg, sc, _chk(input_int8, torch.int8, "input_int8"),
+                                              float(input_scale), _chk(output, torch.float16, "output"),
+                                              rows, cols, group_size, _stream()))
+
+
+def quantize_absmax_int8(input, output, scale, n: int) -> None:
+    """half[n] -> int8[n] + device float scale (reference include/kernels.cuh:30-32)."""
+    _lib.check(_lib.lib().tllm_b200_quantize_absmax_int8(
+        _chk(input, torch.float16, "input"), _chk(output, torch.int8, "output"),
+        _chk(scale, torch.float32, "scale"), n, _stream()))
+
+
+def ternary_gemm(A, nz_B, sign_B, scales_B, C, M: int, N: int, K: int,
+                 group_size: int = GROUP_SIZE) -> None:
+    """C[M,N] = A[M,K] . W^T (reference include/kernels.cuh:37-40)."""
+    nz, sg, sc = _weights(nz_B, sign_B, scales_B)
+    _lib.check(_lib.lib().tllm_b200_gemm(_chk(A, torch.float16, "A"), nz, sg, sc,
+                                         _chk(C, torch.float16, "C"), M, N, K, group_size, _stream()))
