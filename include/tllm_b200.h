@@ -103,6 +103,60 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B,
                    const void* scales_B, void* C,
                    int M, int N, int K, int group_size, void* stream);
 
+
+/* ------------------------------------------------------------------------
+ * Prepared weights (load-time repack).
+ *
+ * The streaming tensor-core GEMV reads a kernel-friendly layout: tiles of 16 rows
+ * x 128 columns, 2 bits per weight arranged as operand selectors, FP16 scales
+ * beside them (ternary_llm_b200/csrc/packed_layout.cuh).  It is derived once per
+ * matrix at load time from the three reference arrays -- the hook sits right
+ * after the reference loader's read_ternary_weight (src/model.cpp:46-60) -- and is
+ * lossless for canonical masks (no sign bit without its nonzero bit), which is
+ * what the reference's packer writes (ternarize/pack.py:135-138):
+ * tllm_b200_weight_unpack returns the original words bit for bit.  A matrix with
+ * stray sign bits is refused (TLLM_ERR_NONCANON) and stays on the general path.
+ * ------------------------------------------------------------------------ */
+
+/* Size in bytes of the packed form of a [rows, cols] matrix (cols % 128 == 0). */
+size_t tllm_b200_packed_bytes(int rows, int cols);
+
+/*
+ * Repack into `packed` (device, 16-byte aligned, >= tllm_b200_packed_bytes).
+ * Runs on `stream` and SYNCHRONISES it before returning (a load-time call).
+ * The first call on a device allocates the library's per-device scratch.
+ */
+int tllm_b200_weight_prepare(const uint32_t* nonzero_masks, const uint32_t* sign_masks,
+                             const void* scales, int rows, int cols, int group_size,
+                             void* packed, size_t packed_size, void* stream);
+
+/* Inverse of prepare: writes canonical nonzero/sign words and the scales. */
+int tllm_b200_weight_unpack(const void* packed, int rows, int cols, int group_size,
+                            uint32_t* nonzero_masks, uint32_t* sign_masks, void* scales,
+                            void* stream);
+
+/*
+ * Associates a prepared buffer with the reference arrays it was made from, keyed
+ * by the nonzero_masks pointer: afterwards tllm_b200_gemv, _gemv_batched,
+ * _gemv_int8 and (for M <= TLLM_MAX_BATCH) _gemm called with that pointer and the
+ * same rows/cols use the prepared weights, so the reference's call sites
+ * (src/transformer.cpp:102-143,199-217,264-278) need no change.  Unregister
+ * before freeing either buffer (reference Model::free_gpu, src/model.cpp:221-250).
+ */
+int tllm_b200_weight_register(const uint32_t* nonzero_masks, const void* packed, int rows, int cols);
+int tllm_b200_weight_unregister(const uint32_t* nonzero_masks);
+
+/*
+ * GEMV directly on prepared weights; same arithmetic contract as tllm_b200_gemv /
+ * _gemv_batched / _gemv_int8.  These kernels keep partial sums of row blocks that
+ * span two SMs in a per-device scratch that the library allocates at its first
+ * use on a device (make one call per device before capturing a CUDA graph).
+ */
+int tllm_b200_gemv_packed(const void* packed, const void* x, void* y,
+                          int batch, int rows, int cols, void* stream);
+int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, float input_scale,
+                               void* y, int rows, int cols, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,6 +24,13 @@ SIGNATURES = {
     "tllm_b200_gemv_int8": (_int, [_vp] * 4 + [ctypes.c_float, _vp] + [_int] * 3 + [_vp]),
     "tllm_b200_quantize_absmax_int8": (_int, [_vp] * 3 + [_int, _vp]),
     "tllm_b200_gemm": (_int, [_vp] * 5 + [_int] * 4 + [_vp]),
+    "tllm_b200_packed_bytes": (ctypes.c_size_t, [_int, _int]),
+    "tllm_b200_weight_prepare": (_int, [_vp] * 3 + [_int] * 3 + [_vp, ctypes.c_size_t, _vp]),
+    "tllm_b200_weight_unpack": (_int, [_vp] + [_int] * 3 + [_vp] * 4),
+    "tllm_b200_weight_register": (_int, [_vp, _vp, _int, _int]),
+    "tllm_b200_weight_unregister": (_int, [_vp]),
+    "tllm_b200_gemv_packed": (_int, [_vp] * 3 + [_int] * 3 + [_vp]),
+    "tllm_b200_gemv_int8_packed": (_int, [_vp, _vp, ctypes.c_float, _vp, _int, _int, _vp]),
 }
 
 

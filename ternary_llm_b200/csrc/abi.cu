@@ -97,6 +97,8 @@ int tllm_b200_gemv_batched(const uint32_t* nz, const uint32_t* sg, const void* s
     if (misaligned(x, 16)) return fail(TLLM_ERR_ALIGN, "activation pointer must be 16-byte aligned");
     if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
     if ((st = check_device())) return st;
+    if (const uint8_t* packed = lookup_packed(nz, rows, cols))
+        return launch_gemv_packed(packed, (const half*)x, (half*)y, batch, rows, cols, (cudaStream_t)stream);
     return launch_gemv_simt(nz, sg, (const half*)scales, (const half*)x, (half*)y, batch, rows, cols,
                             (cudaStream_t)stream);
 }
@@ -117,6 +119,8 @@ int tllm_b200_gemv_int8(const uint32_t* nz, const uint32_t* sg, const void* weig
     if (misaligned(input_int8, 16)) return fail(TLLM_ERR_ALIGN, "int8 activation pointer must be 16-byte aligned");
     if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
     if ((st = check_device())) return st;
+    if (const uint8_t* packed = lookup_packed(nz, rows, cols))
+        return launch_gemv_int8_packed(packed, input_int8, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
     return launch_gemv_int8_simt(nz, sg, (const half*)weight_scales, input_int8, input_scale, (half*)y,
                                  rows, cols, (cudaStream_t)stream);
 }
@@ -142,13 +146,89 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B, 
     if (misaligned(C, 2)) return fail(TLLM_ERR_ALIGN, "C must be 2-byte aligned");
     if ((st = check_device())) return st;
     // Token blocks of at most kMaxBatch rows, each one pass over the weights.
+    const uint8_t* packed = lookup_packed(nz_B, N, K);
     for (int m0 = 0; m0 < M; m0 += kMaxBatch) {
         const int b = (M - m0 < kMaxBatch) ? (M - m0) : kMaxBatch;
+        if (packed) {
+            st = launch_gemv_packed(packed, (const half*)A + (size_t)m0 * K, (half*)C + (size_t)m0 * N, b, N, K,
+                                    (cudaStream_t)stream);
+            if (st) return st;
+            continue;
+        }
         st = launch_gemv_simt(nz_B, sign_B, (const half*)scales_B, (const half*)A + (size_t)m0 * K,
                               (half*)C + (size_t)m0 * N, b, N, K, (cudaStream_t)stream);
         if (st) return st;
     }
     return TLLM_OK;
+}
+
+size_t tllm_b200_packed_bytes(int rows, int cols)
+{
+    if (rows < 1 || cols < kGroup || cols % kGroup) return 0;
+    return packed_bytes(rows, cols);
+}
+
+int tllm_b200_weight_prepare(const uint32_t* nz, const uint32_t* sg, const void* scales, int rows, int cols,
+                             int group_size, void* packed, size_t packed_size, void* stream)
+{
+    int st = check_weights(nz, sg, scales, rows, cols, group_size);
+    if (st) return st;
+    if (!packed) return fail(TLLM_ERR_NULL, "null packed buffer");
+    if (misaligned(packed, 16)) return fail(TLLM_ERR_ALIGN, "packed buffer must be 16-byte aligned");
+    if (packed_size < packed_bytes(rows, cols))
+        return fail(TLLM_ERR_SIZE, "packed buffer holds %zu bytes, %zu needed", packed_size, packed_bytes(rows, cols));
+    if ((st = check_device())) return st;
+    return weight_prepare(nz, sg, (const half*)scales, rows, cols, (uint8_t*)packed, (cudaStream_t)stream);
+}
+
+int tllm_b200_weight_unpack(const void* packed, int rows, int cols, int group_size, uint32_t* nz,
+                            uint32_t* sg, void* scales, void* stream)
+{
+    int st = check_weights(nz, sg, scales, rows, cols, group_size);
+    if (st) return st;
+    if (!packed) return fail(TLLM_ERR_NULL, "null packed buffer");
+    if ((st = check_device())) return st;
+    return weight_unpack((const uint8_t*)packed, rows, cols, nz, sg, (half*)scales, (cudaStream_t)stream);
+}
+
+int tllm_b200_weight_register(const uint32_t* nz, const void* packed, int rows, int cols)
+{
+    if (!nz || !packed) return fail(TLLM_ERR_NULL, "null pointer");
+    if (rows < 1 || cols < kGroup || cols % kGroup) return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d", rows, cols);
+    if (misaligned(packed, 16)) return fail(TLLM_ERR_ALIGN, "packed buffer must be 16-byte aligned");
+    return weight_register(nz, (const uint8_t*)packed, rows, cols);
+}
+
+int tllm_b200_weight_unregister(const uint32_t* nz)
+{
+    if (!nz) return fail(TLLM_ERR_NULL, "null pointer");
+    return weight_unregister(nz);
+}
+
+static int check_packed_call(const void* packed, const void* x, const void* y, int rows, int cols)
+{
+    if (!packed || !x || !y) return fail(TLLM_ERR_NULL, "null pointer");
+    if (rows < 1 || cols < kGroup || cols % kGroup)
+        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: need rows >= 1 and cols a positive multiple of 128", rows, cols);
+    if (misaligned(packed, 16) || misaligned(x, 16)) return fail(TLLM_ERR_ALIGN, "packed and activation pointers must be 16-byte aligned");
+    if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
+    return check_device();
+}
+
+int tllm_b200_gemv_packed(const void* packed, const void* x, void* y, int batch, int rows, int cols, void* stream)
+{
+    int st = check_packed_call(packed, x, y, rows, cols);
+    if (st) return st;
+    if (batch < 1 || batch > kMaxBatch) return fail(TLLM_ERR_BATCH, "batch %d outside 1..%d", batch, kMaxBatch);
+    return launch_gemv_packed((const uint8_t*)packed, (const half*)x, (half*)y, batch, rows, cols, (cudaStream_t)stream);
+}
+
+int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* xq, float input_scale, void* y, int rows,
+                               int cols, void* stream)
+{
+    int st = check_packed_call(packed, xq, y, rows, cols);
+    if (st) return st;
+    return launch_gemv_int8_packed((const uint8_t*)packed, xq, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -27,6 +27,20 @@ int launch_gemv_int8_simt(const uint32_t* nz, const uint32_t* sg, const half* sc
 int launch_quantize_absmax_int8(const half* x, int8_t* q, float* scale, int n,
                                 cudaStream_t stream);
 
+// Tensor-core streaming kernels on the packed layout (gemv_mma.cu).
+size_t packed_bytes(int rows, int cols);
+const uint8_t* lookup_packed(const void* nz, int rows, int cols);
+int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
+                       cudaStream_t stream);
+int launch_gemv_int8_packed(const uint8_t* packed, const int8_t* xq, float in_scale, half* y, int rows,
+                            int cols, cudaStream_t stream);
+int weight_prepare(const uint32_t* nz, const uint32_t* sg, const half* scales, int rows, int cols,
+                   uint8_t* packed, cudaStream_t stream);
+int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint32_t* sg, half* scales,
+                  cudaStream_t stream);
+int weight_register(const void* nz, const uint8_t* packed, int rows, int cols);
+int weight_unregister(const void* nz);
+
 // ---- small device helpers --------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v)
 {

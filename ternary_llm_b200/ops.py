@@ -84,3 +84,67 @@ def ternary_gemm(A, nz_B, sign_B, scales_B, C, M: int, N: int, K: int,
     nz, sg, sc = _weights(nz_B, sign_B, scales_B)
     _lib.check(_lib.lib().tllm_b200_gemm(_chk(A, torch.float16, "A"), nz, sg, sc,
                                          _chk(C, torch.float16, "C"), M, N, K, group_size, _stream()))
+
+
+# --------------------------------------------------------------------------
+# Prepared weights (load-time repack for the streaming tensor-core GEMV)
+# --------------------------------------------------------------------------
+def packed_bytes(rows: int, cols: int) -> int:
+    return int(_lib.lib().tllm_b200_packed_bytes(rows, cols))
+
+
+class PreparedWeight:
+    """One ternary matrix in the packed layout, made from the three reference
+    arrays.  Keeps the source tensors alive and, with register=True, makes the
+    reference-signature entry points (ternary_gemv ...) called with these source
+    tensors use the packed copy, as the C++ engine integration does."""
+
+    def __init__(self, nonzero_masks, sign_masks, scales, rows: int, cols: int, register: bool = True):
+        nz, sg, sc = _weights(nonzero_masks, sign_masks, scales)
+        self.rows, self.cols = rows, cols
+        self.nonzero_masks, self.sign_masks, self.scales = nonzero_masks, sign_masks, scales
+        nbytes = packed_bytes(rows, cols)
+        if nbytes == 0:
+            raise ValueError(f"unsupported shape rows={rows} cols={cols}")
+        self.packed = torch.empty(nbytes, dtype=torch.uint8, device=nonzero_masks.device)
+        _lib.check(_lib.lib().tllm_b200_weight_prepare(nz, sg, sc, rows, cols, GROUP_SIZE,
+                                                       self.packed.data_ptr(), nbytes, _stream()))
+        self.registered = False
+        if register:
+            _lib.check(_lib.lib().tllm_b200_weight_register(nz, self.packed.data_ptr(), rows, cols))
+            self.registered = True
+
+    def unpack(self):
+        """Back to (nonzero_masks, sign_masks, scales) in the reference layout."""
+        dev = self.packed.device
+        nz = torch.empty(self.rows, self.cols // 32, dtype=torch.int32, device=dev)
+        sg = torch.empty_like(nz)
+        sc = torch.empty(self.rows, self.cols // GROUP_SIZE, dtype=torch.float16, device=dev)
+        _lib.check(_lib.lib().tllm_b200_weight_unpack(self.packed.data_ptr(), self.rows, self.cols, GROUP_SIZE,
+                                                      nz.data_ptr(), sg.data_ptr(), sc.data_ptr(), _stream()))
+        return nz, sg, sc
+
+    def release(self):
+        if self.registered:
+            _lib.lib().tllm_b200_weight_unregister(self.nonzero_masks.data_ptr())
+            self.registered = False
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+def ternary_gemv_packed(w: PreparedWeight, input, output, batch: int = 1) -> None:
+    """y[b] = W x[b] on prepared weights, FP16 activations, 1..16 vectors."""
+    _lib.check(_lib.lib().tllm_b200_gemv_packed(w.packed.data_ptr(), _chk(input, torch.float16, "input"),
+                                                _chk(output, torch.float16, "output"), batch, w.rows, w.cols,
+                                                _stream()))
+
+
+def ternary_gemv_int8_packed(w: PreparedWeight, input_int8, input_scale: float, output) -> None:
+    """INT8-activation GEMV on prepared weights."""
+    _lib.check(_lib.lib().tllm_b200_gemv_int8_packed(w.packed.data_ptr(), _chk(input_int8, torch.int8, "input_int8"),
+                                                     float(input_scale), _chk(output, torch.float16, "output"),
+                                                     w.rows, w.cols, _stream()))

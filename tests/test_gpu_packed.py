@@ -1,0 +1,185 @@
+"""GPU tests of the prepared (packed) weight layout and the streaming tensor-core
+GEMV that reads it: the repack is bit-exact and the results meet the same
+tolerance as the general path."""
+import numpy as np
+import pytest
+import torch
+
+import ternary_llm_b200 as tl
+from oracle import oracle
+from tests._util import assert_within, exact_and_bound
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dev(a):
+    if a.dtype == np.uint32:
+        return torch.from_numpy(a.view(np.int32)).to(DEV)
+    return torch.from_numpy(a).to(DEV)
+
+
+def _half_ulp(y64):
+    a = np.maximum(np.abs(y64), 2.0 ** -14)
+    return 0.5 * 2.0 ** (np.floor(np.log2(a)) - 10)
+
+
+def _prep(nz, sg, sc, register=False):
+    n, k = nz.shape[0], nz.shape[1] * 32
+    return tl.PreparedWeight(_dev(nz), _dev(sg), _dev(sc), n, k, register=register)
+
+
+@pytest.mark.parametrize("n,k", [(1, 128), (16, 128), (9, 384), (33, 640), (100, 1024), (1024, 4096), (4096, 4096)])
+def test_repack_round_trip_bit_exact(n, k):
+    nz, sg, sc, _ = oracle.make_case(n, k, seed=n + k)
+    w = _prep(nz, sg, sc)
+    assert w.packed.numel() == ((n + 15) // 16) * (k // 128) * 544
+    nz2, sg2, sc2 = w.unpack()
+    torch.cuda.synchronize()
+    assert (nz2.cpu().numpy().view(np.uint32) == nz).all()
+    assert (sg2.cpu().numpy().view(np.uint32) == sg).all()
+    assert (sc2.cpu().numpy().view(np.uint16) == sc.view(np.uint16)).all()
+    # and the decoded ternary values, through the oracle's unpacker
+    assert (oracle.unpack_bitmasks(nz2.cpu().numpy().view(np.uint32), sg2.cpu().numpy().view(np.uint32))
+            == oracle.unpack_bitmasks(nz, sg)).all()
+
+
+def test_repack_refuses_stray_sign_bits():
+    nz, sg, sc, _ = oracle.make_case(32, 256, seed=1, random_masks=True)
+    with pytest.raises(tl.TllmError) as e:
+        _prep(nz, sg, sc)
+    assert e.value.status == -8
+    # canonicalised words are accepted and decode to the same ternary values
+    w = _prep(nz, sg & nz, sc)
+    nz2, sg2, _ = w.unpack()
+    assert (oracle.unpack_bitmasks(nz2.cpu().numpy().view(np.uint32), sg2.cpu().numpy().view(np.uint32))
+            == oracle.unpack_bitmasks(nz, sg)).all()
+
+
+def _run_packed(w, x):
+    b = x.shape[0]
+    y = torch.full((b, w.rows), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, _dev(x), y, b)
+    torch.cuda.synchronize()
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("n,k", [(1, 128), (16, 128), (9, 384), (33, 640), (64, 1024), (1000, 2048),
+                                 (1024, 4096), (4096, 4096), (8192, 2048), (4096, 11008),
+                                 (14336, 4096), (4096, 14336)])
+def test_gemv_packed_vs_oracle(n, k):
+    nz, sg, sc, x = oracle.make_case(n, k, seed=3 * n + k)
+    w = _prep(nz, sg, sc)
+    y = _run_packed(w, x)
+    y64, bound = exact_and_bound(nz, sg, sc, x)
+    assert not np.isnan(y).any()
+    assert_within(y, y64, bound, f"packed gemv {n}x{k}", slack=_half_ulp(y64))
+
+
+def test_gemv_packed_signed_scales_and_dense_rows():
+    n, k = 64, 512
+    nz, sg, sc, x = oracle.make_case(n, k, seed=9, random_masks=True, signed_scales=True)
+    sg &= nz
+    nz[6], sg[6] = 0xFFFFFFFF, 0xFFFFFFFF       # all +1: largest positive group sums
+    nz[7], sg[7] = 0xFFFFFFFF, 0                # all -1
+    nz[3] = 0
+    sg[3] = 0
+    sc[4] = 0
+    w = _prep(nz, sg, sc)
+    y = _run_packed(w, x)
+    y64, bound = exact_and_bound(nz, sg, sc, x)
+    assert y[0, 3] == 0 and y[0, 4] == 0
+    assert_within(y, y64, bound, "packed edge", slack=_half_ulp(y64))
+
+
+def test_gemv_packed_wide_dynamic_range_and_zero_groups():
+    n, k = 48, 1024
+    nz, sg, sc, x = oracle.make_case(n, k, seed=21)
+    x = x.astype(np.float32)
+    x[0, 5] = 30000.0            # one huge activation in group 0
+    x[0, 128:256] = 0.0          # an all-zero activation group
+    x[0, 256:384] *= 1e-3        # a group of tiny activations
+    x[0, 384:512] = 6e-8         # FP16 subnormals
+    x = x.astype(np.float16)
+    w = _prep(nz, sg, sc)
+    y = _run_packed(w, x)
+    y64, bound = exact_and_bound(nz, sg, sc, x)
+    assert_within(y, y64, bound, "packed dynamic range", slack=_half_ulp(y64))
+
+
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 7, 16])
+def test_gemv_packed_batched(batch):
+    n, k = 528, 1024
+    nz, sg, sc, x = oracle.make_case(n, k, seed=50 + batch, batch=batch)
+    w = _prep(nz, sg, sc)
+    y = _run_packed(w, x)
+    y64, bound = exact_and_bound(nz, sg, sc, x)
+    assert_within(y, y64, bound, f"packed batched {batch}", slack=_half_ulp(y64))
+
+
+@pytest.mark.parametrize("n,k", [(16, 128), (100, 512), (1024, 4096), (4096, 11008)])
+def test_gemv_int8_packed_vs_oracle(n, k):
+    nz, sg, sc, x = oracle.make_case(n, k, seed=n * 5 + k, signed_scales=True)
+    q, s = oracle.quantize_absmax_int8(x[0])
+    w = _prep(nz, sg, sc)
+    y = torch.zeros(n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_int8_packed(w, _dev(q), float(s), y)
+    torch.cuda.synchronize()
+    xs = q.astype(np.float64) * np.float64(s)
+    y64 = oracle.ternary_matvec(nz, sg, sc, xs, 128, np.float64)
+    bound = oracle.tolerance_bound(nz, sg, sc, xs, 128)
+    assert_within(y.cpu().numpy(), y64, bound, f"packed int8 {n}x{k}", slack=_half_ulp(y64))
+
+
+def test_registered_weights_route_reference_signatures():
+    n, k = 512, 2048
+    nz, sg, sc, x = oracle.make_case(n, k, seed=77, batch=3)
+    dnz, dsg, dsc, dx = _dev(nz), _dev(sg), _dev(sc), _dev(x)
+    y_general = torch.zeros(3, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_batched(dnz, dsg, dsc, dx, y_general, 3, n, k)
+    w = tl.PreparedWeight(dnz, dsg, dsc, n, k, register=True)
+    y_fast = torch.zeros(3, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_batched(dnz, dsg, dsc, dx, y_fast, 3, n, k)       # same call, now packed
+    y_direct = torch.zeros(3, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, dx, y_direct, 3)
+    c = torch.zeros(3, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemm(dx, dnz, dsg, dsc, c, 3, n, k)
+    torch.cuda.synchronize()
+    assert torch.equal(y_fast, y_direct) and torch.equal(c, y_direct)
+    y64, bound = exact_and_bound(nz, sg, sc, x)
+    assert_within(y_fast.cpu().numpy(), y64, bound, "registered", slack=_half_ulp(y64))
+    assert_within(y_general.cpu().numpy(), y64, bound, "general", slack=_half_ulp(y64))
+    w.release()
+    y_again = torch.zeros(3, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_batched(dnz, dsg, dsc, dx, y_again, 3, n, k)       # back on the general path
+    torch.cuda.synchronize()
+    assert torch.equal(y_again, y_general)
+
+
+def test_gemv_packed_is_deterministic_and_reusable():
+    n, k = 4096, 4096
+    nz, sg, sc, x = oracle.make_case(n, k, seed=123)
+    w = _prep(nz, sg, sc)
+    dx = _dev(x)
+    outs = []
+    for _ in range(70):          # more launches than scratch tickets: arrival counters must self-reset
+        y = torch.zeros(1, n, dtype=torch.float16, device=DEV)
+        tl.ternary_gemv_packed(w, dx, y, 1)
+        outs.append(y)
+    torch.cuda.synchronize()
+    for y in outs[1:]:
+        assert torch.equal(y, outs[0])
+
+
+def test_gemv_packed_linearity_at_full_size():
+    """Size-independent property at a benchmark shape: W(2x) = 2 W(x) exactly
+    (power-of-two scaling commutes with every rounding step short of overflow)."""
+    n, k = 14336, 4096
+    nz, sg, sc = tl.pack.random_ternary_weight(n, k, seed=4)
+    w = _prep(nz, sg, sc)
+    x = np.random.default_rng(8).standard_normal((1, k)).astype(np.float16)
+    y1 = _run_packed(w, x)
+    y2 = _run_packed(w, (2 * x.astype(np.float32)).astype(np.float16))
+    assert np.array_equal(2 * y1.astype(np.float32), y2.astype(np.float32))
+    yn = _run_packed(w, -x)
+    assert np.array_equal(-y1, yn)
