@@ -157,6 +157,15 @@ int tllm_b200_gemv_packed(const void* packed, const void* x, void* y,
 int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, float input_scale,
                                void* y, int rows, int cols, void* stream);
 
+/*
+ * Device-side waits in the kernels are bounded; one that expires sets a flag on
+ * the device and the kernel returns early (its output is then invalid).  This
+ * call SYNCHRONISES `stream`, returns TLLM_ERR_TIMEOUT if the flag was set since
+ * the last check (and clears it), else TLLM_OK.  No counterpart in the reference,
+ * which checks no errors.
+ */
+int tllm_b200_check_device_errors(void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -231,4 +231,11 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* xq, float input
     return launch_gemv_int8_packed((const uint8_t*)packed, xq, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
 }
 
+int tllm_b200_check_device_errors(void* stream)
+{
+    int st = check_device();
+    if (st) return st;
+    return device_error_check((cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -40,6 +40,7 @@ int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint3
                   cudaStream_t stream);
 int weight_register(const void* nz, const uint8_t* packed, int rows, int cols);
 int weight_unregister(const void* nz);
+int device_error_check(cudaStream_t stream);
 
 // ---- small device helpers --------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v)

@@ -17,20 +17,22 @@
 //   group maximum is at the level of FP32 accumulation rounding itself.
 //   INT8 activations (ternary_gemv_int8 semantics): B is the int8 vector as is.
 //
-// Work decomposition: a unit is one 16-row block x 4 scale groups (2176 bytes of
-// packed weights).  Units are dealt to CTAs in contiguous, equal ranges (one CTA
-// per SM), so K is split across CTAs where rows alone would not balance 148 SMs;
-// inside a CTA the units go round-robin to 16 warps.  Each warp streams its units
-// through a private cp.async ring (no cross-warp synchronisation on the data
-// path).  Per-unit partial sums are reduced in a fixed order; a 16-row block that
-// spans two or more CTAs is finished by whichever CTA arrives last, which sums
-// the partial records in CTA order, so results do not depend on timing.
+// Work decomposition: the matrix is a linear array of tiles (16 rows x one scale
+// group, 544 bytes; row-block major).  Tiles are dealt to CTAs (one per SM) and,
+// inside a CTA, to 16 warps in contiguous, equal ranges, so K is split wherever
+// rows alone would not balance 148 SMs.  A warp's range is contiguous in memory:
+// it arrives through the warp's private two-slot ring of bulk-TMA copies
+// (cp.async.bulk + mbarrier, 4 tiles per slot), all issued at kernel start when
+// the range fits.  Partial sums of a 16-row block are combined in a fixed order:
+// first over the warps of a CTA, then, for a block that spans several CTAs, by
+// whichever CTA arrives last, which adds the CTAs' records in CTA order.  Results
+// therefore do not depend on timing.
 //
-// Launches carry the programmatic-dependent-launch attribute: the weight prefetch
-// is issued before griddepcontrol.wait (weights are constants), activations are
-// read and outputs written after it.  CTAs are sized (512 threads, <= 64
-// registers, about half of shared memory) so that the next GEMV's CTAs can become
-// resident while this one drains.
+// Launches carry the programmatic-dependent-launch attribute: the weight fetch is
+// issued before griddepcontrol.wait (weights are constants), activations are read
+// and outputs written after it, so a GEMV's weight stream starts while the kernel
+// before it in the stream drains.  Every mbarrier wait is bounded; a wait that
+// gives up records TLLM_ERR_TIMEOUT in a device flag and the kernel returns.
 #include <mutex>
 #include <unordered_map>
 
@@ -39,12 +41,17 @@
 
 namespace tllm {
 
-constexpr int kWarps = 16;
+#ifndef TLLM_GEMV_WARPS_LOG2
+#define TLLM_GEMV_WARPS_LOG2 4
+#endif
+constexpr int kWarpsLog2 = TLLM_GEMV_WARPS_LOG2;
+constexpr int kWarps = 1 << kWarpsLog2;
 constexpr int kThreads = kWarps * 32;
-constexpr int kUnitGroups = 4;                       // scale groups per unit
-constexpr int kUnitBytes = kUnitGroups * kTileBytes; // 2176
-constexpr int kRing = 2;                             // units in flight per warp
-constexpr int kTickets = 64;                         // independent scratch regions
+constexpr int kCtasPerSm = (kWarps <= 16) ? 2 : 1;   // co-residency target for __launch_bounds__
+constexpr int kSlotTiles = 4;                         // tiles per ring slot
+constexpr int kSlotBytes = kSlotTiles * kTileBytes;   // 2176
+constexpr int kRing = 2;                              // slots per warp
+constexpr int kTickets = 64;                          // independent scratch regions
 constexpr int kMaxCtas = 256;
 
 enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2 };
@@ -54,27 +61,63 @@ struct GemvArgs {
     const void* x;          // half [batch, cols] or int8 [cols]
     half* y;                // half [batch, rows]
     float in_scale;         // INT8 mode: activation scale
-    int rows, cols, groups; // groups = cols / 128
-    int upr;                // units per row block = ceil(groups / 4)
-    int nrb;                // row blocks = ceil(rows / 16)
+    int rows, cols, groups; // groups = cols / 128 = tiles per row block
     int batch;              // 1 or 2 vectors handled by this launch
-    long long total_units;
-    int max_units_per_cta;
+    int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
+    int aligned;            // 1: items are whole row blocks (no block spans two CTAs); 0: items are tiles
     float* ws;              // [gridDim.x][2][16][2] partial records of this ticket
-    int* counters;          // [nrb] arrival counters of this ticket (zero between launches)
+    int* counters;          // [row blocks] arrival counters of this ticket (zero between launches)
+    int* err;               // device error flag (0 = none)
     // shared memory carve-up (byte offsets)
-    int off_xfac, off_part, off_ring, off_flags;
+    int off_xfac, off_part, off_ring, off_bar;
 };
 
+#ifdef TLLM_PROFILE_PHASES
+__device__ unsigned long long g_phase_ns[kMaxCtas * 16];
+__device__ __forceinline__ void phase_mark(int k)
+{
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_phase_ns[blockIdx.x * 16 + k] = t;
+    }
+}
+#define PHASE(k) phase_mark(k)
+#else
+#define PHASE(k)
+#endif
+
+// ---- PTX helpers ------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count)
 {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait (about a second at most); false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (int i = 0; i < (1 << 22); i++)
+        if (mbar_try(bar, parity)) return true;
+    return false;
+}
+// Bulk copy global -> this CTA's shared memory, completion counted on `bar`.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t lo, uint32_t hi, uint32_t sel)
 {
@@ -83,126 +126,222 @@ __device__ __forceinline__ uint32_t prmt(uint32_t lo, uint32_t hi, uint32_t sel)
     return r;
 }
 
-template <bool BSIGNED>
+// D = A.B (+ D when ACC).  The zero accumulator is passed as immediates so that no
+// register has to be cleared per group.
+template <bool BSIGNED, bool ACC>
 __device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                      uint32_t b0, uint32_t b1)
 {
-    if (BSIGNED)
-        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    else
-        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    if (ACC) {
+        if (BSIGNED)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        if (BSIGNED)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    }
 }
 
-// First unit index of CTA c when `total` units are dealt to `n` CTAs.
-__host__ __device__ inline long long cta_start(long long c, long long total, long long n) { return c * total / n; }
-// CTA that owns unit u.
-__host__ __device__ inline int cta_of_unit(long long u, long long total, long long n)
+// Contiguous equal split of `total` items over `parts`: with q = total / parts and
+// r = total % parts (host-computed), part c owns [c*q + min(c,r), ...): the first r
+// parts hold q+1 items.  32-bit arithmetic only.
+__device__ __forceinline__ int part_start(int c, int q, int r) { return c * q + min(c, r); }
+__device__ __forceinline__ int part_of(int u, int q, int r)
 {
-    return (int)(((u + 1) * n - 1) / total);
+    const int big = r * (q + 1);
+    return (u < big) ? (int)((unsigned)u / (unsigned)(q + 1)) : r + (int)((unsigned)(u - big) / (unsigned)q);
 }
+// The n tiles of a CTA over its warps: warp w owns [w*n/kWarps, (w+1)*n/kWarps).
+__device__ __forceinline__ int warp_start(int w, int n) { return (w * n) >> kWarpsLog2; }
+__device__ __forceinline__ int warp_of(int i, int n) { return (int)((unsigned)((i + 1) * kWarps - 1) / (unsigned)n); }
 
 // ---------------------------------------------------------------------------
 // Activation staging
 // ---------------------------------------------------------------------------
-// FP16 -> block fixed point digits in B-fragment order.  LANES = 16 (one vector,
-// columns [d0 d1 d2 1]) or 32 (two vectors).  xdig is uint32 [groups][4 steps][LANES][2].
+// Three digit words (byte c of four consecutive q values) for one quad of activations.
+__device__ __forceinline__ void quad_digits(float v0, float v1, float v2, float v3, float up,
+                                            uint32_t& w0, uint32_t& w1, uint32_t& w2)
+{
+    const uint32_t q0 = (uint32_t)(__float2int_rn(v0 * up) + (1 << 23));
+    const uint32_t q1 = (uint32_t)(__float2int_rn(v1 * up) + (1 << 23));
+    const uint32_t q2 = (uint32_t)(__float2int_rn(v2 * up) + (1 << 23));
+    const uint32_t q3 = (uint32_t)(__float2int_rn(v3 * up) + (1 << 23));
+    const uint32_t u = __byte_perm(q0, q1, 0x5140), v = __byte_perm(q2, q3, 0x5140);
+    const uint32_t r = __byte_perm(q0, q1, 0x0062), s = __byte_perm(q2, q3, 0x0062);
+    w0 = __byte_perm(u, v, 0x5410);
+    w1 = __byte_perm(u, v, 0x7632);
+    w2 = __byte_perm(r, s, 0x5410);
+}
+
+// FP16 -> block fixed point digits in B-operand order.  LANES = 16 (one vector,
+// columns [d0 d1 d2 1]) or 32 (two vectors).  xdig is uint32 [groups][2 step pairs]
+// [LANES][4]: the four words of lane l = 4*column + t are (b0,b1) of k32 step 2p and
+// (b0,b1) of step 2p+1, so one 128-bit shared load feeds two MMAs.
+// Each thread converts 8 consecutive activations (one 128-bit load); the 16 lanes of
+// a half-warp cover one scale group and agree on its exponent with four shuffles.
 template <int LANES>
 __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols, int groups, int batch,
-                                            uint32_t* xdig, float* xfac, int warp, int lane)
+                                            uint32_t* xdig, float* xfac, int tid)
 {
-    for (int g = warp; g < groups; g += kWarps) {
-        for (int b = 0; b < batch; b++) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(x + (size_t)b * cols + (size_t)g * kGroup + lane * 4);
-            const float2 v01 = __half22float2(*reinterpret_cast<const half2*>(&raw.x));
-            const float2 v23 = __half22float2(*reinterpret_cast<const half2*>(&raw.y));
-            float m = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
-            m = warp_max(m);
-            // 2^e > m; FP16 inputs keep e within [-23, 16]
-            int e = (int)((__float_as_uint(m) >> 23) & 0xffu) - 126;
-            e = max(e, -24);
-            const float up = (m > 0.f) ? __uint_as_float((uint32_t)(22 - e + 127) << 23) : 0.f;
-            const float dn = (m > 0.f) ? __uint_as_float((uint32_t)(e - 22 + 127) << 23) : 0.f;
-            const uint32_t q0 = (uint32_t)(__float2int_rn(v01.x * up) + (1 << 23));
-            const uint32_t q1 = (uint32_t)(__float2int_rn(v01.y * up) + (1 << 23));
-            const uint32_t q2 = (uint32_t)(__float2int_rn(v23.x * up) + (1 << 23));
-            const uint32_t q3 = (uint32_t)(__float2int_rn(v23.y * up) + (1 << 23));
-            const uint32_t u = __byte_perm(q0, q1, 0x5140), v = __byte_perm(q2, q3, 0x5140);
-            const uint32_t r = __byte_perm(q0, q1, 0x0062), s = __byte_perm(q2, q3, 0x0062);
-            const uint32_t w0 = __byte_perm(u, v, 0x5410), w1 = __byte_perm(u, v, 0x7632);
-            const uint32_t w2 = __byte_perm(r, s, 0x5410);
-            // lane holds group columns 4*lane .. 4*lane+3: step m = lane/8, k-slot 4*(lane%8)
-            const int m4 = lane >> 3, tq = lane & 7;
-            uint32_t* base = xdig + (((size_t)g * 4 + m4) * LANES) * 2 + (tq & 3) * 2 + (tq >> 2);
-            const int c0 = b * 4;                       // columns 4b .. 4b+3 of this vector
-            base[(c0 + 0) * 8] = w0;
-            base[(c0 + 1) * 8] = w1;
-            base[(c0 + 2) * 8] = w2;
-            base[(c0 + 3) * 8] = 0x01010101u;
-            if (lane == 0) xfac[b * groups + g] = dn;
+    const int per_vec = cols >> 3;                 // 8-element items per vector (multiple of 16)
+    const int items = per_vec * batch;
+    const int l16 = tid & 15;
+    for (int base = 0; base < items; base += kThreads) {
+        const int item = base + tid;
+        const bool valid = item < items;           // uniform per half-warp
+        const int ic = valid ? item : 0;
+        const int b = (ic >= per_vec) ? 1 : 0;
+        const int e8 = ic - b * per_vec;           // item index inside the vector
+        const int g = e8 >> 4;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + e8);
+        const float2 f0 = __half22float2(*reinterpret_cast<const half2*>(&raw.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const half2*>(&raw.y));
+        const float2 f2 = __half22float2(*reinterpret_cast<const half2*>(&raw.z));
+        const float2 f3 = __half22float2(*reinterpret_cast<const half2*>(&raw.w));
+        float m = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))),
+                        fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // 2^e > m; FP16 inputs keep e within [-23, 16]
+        const int e = max((int)((__float_as_uint(m) >> 23) & 0xffu) - 126, -24);
+        const float up = (m > 0.f) ? __uint_as_float((uint32_t)(22 - e + 127) << 23) : 0.f;
+        const float dn = (m > 0.f) ? __uint_as_float((uint32_t)(e - 22 + 127) << 23) : 0.f;
+        uint32_t w[2][3];
+        quad_digits(f0.x, f0.y, f1.x, f1.y, up, w[0][0], w[0][1], w[0][2]);
+        quad_digits(f2.x, f2.y, f3.x, f3.y, up, w[1][0], w[1][1], w[1][2]);
+        if (valid) {
+            // quads 2*l16 and 2*l16+1 of the group: k32 step m4 = quad/8, k-slot 4*(quad%8):
+            // slots 0..15 are b0 of t = quad%8, slots 16..31 are b1 of t = quad%8 - 4
+            const int quad = 2 * l16, m4 = quad >> 3, tq = quad & 7;
+            uint32_t* p = xdig + ((g * 2 + (m4 >> 1)) * LANES + b * 16 + (tq & 3)) * 4 + (m4 & 1) * 2 + (tq >> 2);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {           // second quad: next t, same half
+                p[h * 4 + 0 * 16] = w[h][0];
+                p[h * 4 + 1 * 16] = w[h][1];
+                p[h * 4 + 2 * 16] = w[h][2];
+                p[h * 4 + 3 * 16] = 0x01010101u;
+            }
+            if (l16 == 0) xfac[b * groups + g] = dn;
         }
     }
+}
+
+// One tile (one scale group of a 16-row block): four k32 MMA steps.  Returns the
+// weighted integer group sums of rows gq (p0) and gq+8 (p1).
+//   xq4: FP16 modes, this lane's 128-bit B words of the group (step pairs at [0], [LANES])
+//   xw : INT8 mode, the group's 32 activation words offset by t
+template <bool I8, int LANES>
+__device__ __forceinline__ void tile_mma(const uint8_t* tp, int lane, const uint4* xq4, const uint32_t* xw,
+                                         int mulA, int mulB, int& p0, int& p1)
+{
+    const uint2 ca = *reinterpret_cast<const uint2*>(tp + lane * 8);
+    const uint2 cb = *reinterpret_cast<const uint2*>(tp + 256 + lane * 8);
+    uint4 b01, b23;
+    if (I8) {
+        b01 = make_uint4(xw[0], xw[4], xw[8], xw[12]);
+        b23 = make_uint4(xw[16], xw[20], xw[24], xw[28]);
+    } else {
+        b01 = xq4[0];
+        b23 = xq4[LANES];
+    }
+    int d[4];
+    imma<I8, false>(d, prmt(kTabA_lo, kTabA_hi, ca.x), prmt(kTabA_lo, kTabA_hi, cb.x),
+                    prmt(kTabB_lo, kTabB_hi, ca.x), prmt(kTabB_lo, kTabB_hi, cb.x), b01.x, b01.y);
+    {
+        const uint32_t s0 = ca.x >> 16, s1 = cb.x >> 16;
+        imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, s0), prmt(kTabA_lo, kTabA_hi, s1),
+                       prmt(kTabB_lo, kTabB_hi, s0), prmt(kTabB_lo, kTabB_hi, s1), b01.z, b01.w);
+    }
+    imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, ca.y), prmt(kTabA_lo, kTabA_hi, cb.y),
+                   prmt(kTabB_lo, kTabB_hi, ca.y), prmt(kTabB_lo, kTabB_hi, cb.y), b23.x, b23.y);
+    {
+        const uint32_t s0 = ca.y >> 16, s1 = cb.y >> 16;
+        imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, s0), prmt(kTabA_lo, kTabA_hi, s1),
+                       prmt(kTabB_lo, kTabB_hi, s0), prmt(kTabB_lo, kTabB_hi, s1), b23.z, b23.w);
+    }
+    p0 = d[1] * mulA + d[0] * mulB;
+    p1 = d[3] * mulA + d[2] * mulB;
 }
 
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs a)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const GemvArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr bool I8 = (MODE == kI8);
     constexpr int LANES = (MODE == kF16B2) ? 32 : 16;
 
     asm volatile("griddepcontrol.launch_dependents;");
+    PHASE(0);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nctas = gridDim.x;
-    const long long u0 = cta_start(blockIdx.x, a.total_units, nctas);
-    const long long u1 = cta_start(blockIdx.x + 1, a.total_units, nctas);
-    const int nunits = (int)(u1 - u0);
+    const int G = a.groups;
+    const int per = a.aligned ? G : 1;                                     // tiles per partition item
+    const int t0 = part_start(blockIdx.x, a.part_q, a.part_r) * per;      // first tile of this CTA
+    const int n = (a.part_q + ((int)blockIdx.x < a.part_r ? 1 : 0)) * per; // tiles of this CTA
+    PHASE(8);
+    const int rb_first = (int)((unsigned)t0 / (unsigned)G);
+    const int rb_last = (int)((unsigned)(t0 + n - 1) / (unsigned)G);
 
     uint32_t* xstage = reinterpret_cast<uint32_t*>(smem);              // digits, or the int8 vector
     float* xfac = reinterpret_cast<float*>(smem + a.off_xfac);
-    float* part = reinterpret_cast<float*>(smem + a.off_part);         // [unit][16 rows][2]
-    uint8_t* ring = smem + a.off_ring + (size_t)warp * kRing * kUnitBytes;
-    int* flags = reinterpret_cast<int*>(smem + a.off_flags);
+    float* part = reinterpret_cast<float*>(smem + a.off_part);         // [segment][16 rows][2]
+    const uint32_t ring = smem_addr(smem + a.off_ring) + warp * (kRing * kSlotBytes);
+    const uint8_t* ring_p = smem + a.off_ring + warp * (kRing * kSlotBytes);
+    const uint32_t bar = smem_addr(smem + a.off_bar) + warp * (kRing * 8);
 
-    // ---- weight prefetch: this warp's first kRing units -----------------------
-    auto unit_src = [&](int i, int& ng) -> const uint8_t* {
-        const long long u = u0 + i;
-        const int rb = (int)(u / a.upr), c = (int)(u % a.upr);
-        const int g0 = c * kUnitGroups;
-        ng = min(kUnitGroups, a.groups - g0);
-        return a.packed + ((size_t)rb * a.groups + g0) * kTileBytes;
-    };
-    auto issue = [&](int i, int slot) {
-        if (i < nunits) {
-            int ng;
-            const uint8_t* src = unit_src(i, ng);
-            const uint32_t dst = smem_addr(ring + (size_t)slot * kUnitBytes);
-            const int chunks = ng * (kTileBytes / 16);
-            for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 16, src + (size_t)c * 16);
-        }
-        cp_async_commit();     // one group per slot fill, possibly empty
-    };
+    // ---- this warp's tile range and its weight fetch ----------------------------
+    const int w0 = t0 + warp_start(warp, n), w1 = t0 + warp_start(warp + 1, n);
+    const int nw = w1 - w0;                                  // may be 0 for tiny problems
+    const int nchunks = (nw + kSlotTiles - 1) / kSlotTiles;
+    if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kRing; s++) issue(warp + s * kWarps, s);
+        for (int s = 0; s < kRing; s++) mbar_init(bar + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    PHASE(9);
+    auto fetch = [&](int chunk) {                            // lane 0 only
+        const int first = w0 + chunk * kSlotTiles;
+        const uint32_t bytes = (uint32_t)min(kSlotTiles, w1 - first) * kTileBytes;
+        const int slot = chunk % kRing;
+        mbar_expect_tx(bar + slot * 8, bytes);
+        bulk_g2s(ring + slot * kSlotBytes, a.packed + (size_t)first * kTileBytes, bytes, bar + slot * 8);
+    };
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kRing; s++)
+            if (s < nchunks) fetch(s);
+    }
 
     // ---- everything below may depend on the previous kernel in the stream -------
+    PHASE(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    PHASE(2);
 
     if (I8) {
         const int n16 = a.cols / 16;
         const uint4* src = reinterpret_cast<const uint4*>(a.x);
         for (int i = tid; i < n16; i += kThreads) reinterpret_cast<uint4*>(xstage)[i] = __ldg(src + i);
     } else {
-        stage_x_f16<LANES>(reinterpret_cast<const half*>(a.x), a.cols, a.groups, a.batch, xstage, xfac, warp, lane);
+        stage_x_f16<LANES>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xfac, tid);
     }
     __syncthreads();
+    PHASE(3);
 
     // ---- per-lane constants ------------------------------------------------------
     const int t = lane & 3, gq = lane >> 2;
@@ -215,121 +354,146 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         mulA = !live ? 0 : ((t & 1) ? -(1 << 23) : 256);
         mulB = !live ? 0 : ((t & 1) ? 65536 : 1);
     }
-    const int bsel = (MODE == kF16B2) ? (t >> 1) : 0;
-    const float* xf = xfac + bsel * a.groups;
-    const int xlane = (LANES == 32) ? lane : (lane & 15);
+    const float* xf = xfac + ((MODE == kF16B2) ? (t >> 1) : 0) * G;
+    const uint4* xq4 = reinterpret_cast<const uint4*>(xstage) + ((LANES == 32) ? lane : (lane & 15));
+    const uint32_t* xw = xstage + t;
 
-    // ---- main loop: this warp's units -----------------------------------------
-    int it = 0;
-    for (int i = warp; i < nunits; i += kWarps, it++) {
-        const int slot = it % kRing;
-        cp_async_wait<kRing - 1>();
-        __syncwarp();
-        int ng;
-        const long long u = u0 + i;
-        const int g0 = (int)(u % a.upr) * kUnitGroups;
-        ng = min(kUnitGroups, a.groups - g0);
-        const uint8_t* tile = ring + (size_t)slot * kUnitBytes;
-        float acc0 = 0.f, acc1 = 0.f;       // rows gq and gq+8
+    // ---- main loop: this warp's tiles, four per ring slot --------------------------
+    int rb = (int)((unsigned)w0 / (unsigned)G);
+    int g = w0 - rb * G;
+    int seg = (rb - rb_first) + warp;        // partial-sum slot: unique per (warp, row block), ascending
+    float acc0 = 0.f, acc1 = 0.f;            // rows gq and gq+8 of row block rb
+    bool dirty = false, ok = true;
 
-#pragma unroll 2
-        for (int j = 0; j < ng; j++) {
-            const uint8_t* tp = tile + j * kTileBytes;
-            const uint2 ca = *reinterpret_cast<const uint2*>(tp + lane * 8);
-            const uint2 cb = *reinterpret_cast<const uint2*>(tp + 256 + lane * 8);
-            const half2 sc2 = *reinterpret_cast<const half2*>(tp + kTileCodeBytes + gq * 4);
-            const int g = g0 + j;
-            int dE[4] = {0, 0, 0, 0}, dO[4] = {0, 0, 0, 0};
-#pragma unroll
-            for (int m = 0; m < 4; m++) {
-                const uint32_t wa = (m < 2) ? ca.x : ca.y, wb = (m < 2) ? cb.x : cb.y;
-                const uint32_t s0 = (m & 1) ? (wa >> 16) : wa, s1 = (m & 1) ? (wb >> 16) : wb;
-                const uint32_t a0 = prmt(kTabA_lo, kTabA_hi, s0), a2 = prmt(kTabB_lo, kTabB_hi, s0);
-                const uint32_t a1 = prmt(kTabA_lo, kTabA_hi, s1), a3 = prmt(kTabB_lo, kTabB_hi, s1);
-                uint32_t b0, b1;
-                if (I8) {
-                    const uint32_t* xw = xstage + g * 32 + m * 8 + t;
-                    b0 = xw[0];
-                    b1 = xw[4];
-                } else {
-                    const uint2 bb = *reinterpret_cast<const uint2*>(xstage + (((size_t)g * 4 + m) * LANES + xlane) * 2);
-                    b0 = bb.x;
-                    b1 = bb.y;
-                }
-                if (m & 1) imma<I8>(dO, a0, a1, a2, a3, b0, b1);
-                else imma<I8>(dE, a0, a1, a2, a3, b0, b1);
-            }
-            const int p0 = (dE[1] + dO[1]) * mulA + (dE[0] + dO[0]) * mulB;
-            const int p1 = (dE[3] + dO[3]) * mulA + (dE[2] + dO[2]) * mulB;
-            const float2 sc = __half22float2(sc2);
-            const float f = I8 ? 1.0f : xf[g];
-            acc0 = fmaf((float)p0, sc.x * f, acc0);
-            acc1 = fmaf((float)p1, sc.y * f, acc1);
-        }
+    auto flush = [&]() {
         // lanes t and t^1 hold the two digit halves of one vector
         acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
         acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        float* pu = part + seg * 32;
         if (I8 || MODE == kF16B1) {
             if (t == 0) {
-                part[((size_t)i * 16 + gq) * 2] = acc0;
-                part[((size_t)i * 16 + gq + 8) * 2] = acc1;
+                pu[gq * 2] = acc0;
+                pu[(gq + 8) * 2] = acc1;
             }
         } else if ((t & 1) == 0) {
-            part[((size_t)i * 16 + gq) * 2 + (t >> 1)] = acc0;
-            part[((size_t)i * 16 + gq + 8) * 2 + (t >> 1)] = acc1;
+            pu[gq * 2 + (t >> 1)] = acc0;
+            pu[(gq + 8) * 2 + (t >> 1)] = acc1;
         }
-        __syncwarp();
-        issue(i + kRing * kWarps, slot);
+        acc0 = acc1 = 0.f;
+        dirty = false;
+    };
+
+    for (int c = 0; c < nchunks && ok; c++) {
+        const int slot = c % kRing;
+        ok = mbar_wait(bar + slot * 8, (uint32_t)(c / kRing) & 1u);
+        if (!ok) break;
+        const uint8_t* tile = ring_p + slot * kSlotBytes;
+        const int nt = min(kSlotTiles, nw - c * kSlotTiles);
+        if (nt == kSlotTiles && g + kSlotTiles <= G) {
+            // common case: four tiles of one row block, straight-line code with
+            // compile-time offsets and four independent MMA chains
+            const uint4* xg = xq4 + g * (2 * LANES);
+            const uint32_t* xwg = xw + g * 32;
+            int p[kSlotTiles][2];
+#pragma unroll
+            for (int q = 0; q < kSlotTiles; q++)
+                tile_mma<I8, LANES>(tile + q * kTileBytes, lane, xg + q * (2 * LANES), xwg + q * 32, mulA, mulB,
+                                    p[q][0], p[q][1]);
+#pragma unroll
+            for (int q = 0; q < kSlotTiles; q++) {
+                const float2 sc = __half22float2(
+                    *reinterpret_cast<const half2*>(tile + q * kTileBytes + kTileCodeBytes + gq * 4));
+                const float f = I8 ? 1.0f : xf[g + q];
+                acc0 = fmaf((float)p[q][0], sc.x * f, acc0);
+                acc1 = fmaf((float)p[q][1], sc.y * f, acc1);
+            }
+            g += kSlotTiles;
+            dirty = true;
+            if (g == G) {
+                flush();
+                g = 0;
+                rb++;
+                seg++;
+            }
+        } else {
+            // ragged slot (end of the warp's range or a row-block boundary inside it)
+            for (int j = 0; j < nt; j++) {
+                const uint8_t* tp = tile + j * kTileBytes;
+                int pa0, pa1;
+                tile_mma<I8, LANES>(tp, lane, xq4 + g * (2 * LANES), xw + g * 32, mulA, mulB, pa0, pa1);
+                const float2 sa = __half22float2(*reinterpret_cast<const half2*>(tp + kTileCodeBytes + gq * 4));
+                const float fa = I8 ? 1.0f : xf[g];
+                acc0 = fmaf((float)pa0, sa.x * fa, acc0);
+                acc1 = fmaf((float)pa1, sa.y * fa, acc1);
+                g++;
+                dirty = true;
+                if (g == G) {                    // row block finished (for this warp)
+                    flush();
+                    g = 0;
+                    rb++;
+                    seg++;
+                }
+            }
+        }
+        if (c + kRing < nchunks) {           // refill this slot with the chunk two ahead
+            __syncwarp();
+            if (lane == 0) fetch(c + kRing);
+        }
     }
-    cp_async_wait<0>();
+    if (dirty) flush();
+    if (!ok && lane == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+    PHASE(4);
     __syncthreads();
+    PHASE(5);
 
-    // ---- reduction over units, row block by row block ------------------------------
-    if (nunits == 0) return;
+    // ---- reduction: warps of this CTA, then CTAs, row block by row block -----------
     const int nb = (MODE == kF16B2) ? a.batch : 1;
-    const int rb_first = (int)(u0 / a.upr), rb_last = (int)((u1 - 1) / a.upr);
     const float oscale = I8 ? a.in_scale : 1.0f;
-    float* myrec = a.ws + (size_t)blockIdx.x * 2 * 32;
-    if (tid < 2) flags[tid] = 0;
-    __syncthreads();
+    float* myrec = a.ws + (size_t)blockIdx.x * 64;
 
-    for (int rb = rb_first + (tid >> 5); rb <= rb_last; rb += kWarps) {
+    for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
         const int row = lane >> 1, b = lane & 1;
-        const long long ua = max(u0, (long long)rb * a.upr), ub = min(u1, (long long)(rb + 1) * a.upr);
+        const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);     // this CTA's tiles of the block
+        const int wa = warp_of(ta - t0, n), wb = warp_of(tb - 1 - t0, n);
         float s = 0.f;
-        for (long long u = ua; u < ub; u++) s += part[((size_t)(u - u0) * 16 + row) * 2 + b];
-        const bool full = (ua == (long long)rb * a.upr) && (ub == (long long)(rb + 1) * a.upr);
+        for (int w = wa; w <= wb; w++)
+            if (warp_start(w + 1, n) > warp_start(w, n))       // warps without tiles wrote nothing
+                s += part[((r_b - rb_first) + w) * 32 + lane];
+        const bool full = (tb - ta == G);
+        const int r = r_b * 16 + row;
         if (full) {
-            const int r = rb * 16 + row;
             if (r < a.rows && b < nb) a.y[(size_t)b * a.rows + r] = __float2half_rn(s * oscale);
         } else {
-            const int k = (rb == rb_first) ? 0 : 1;
+            // this row block is shared with neighbouring CTAs: publish the partial sums;
+            // the contributor that arrives last adds all records in CTA order
+            const int k = (r_b == rb_first) ? 0 : 1;
             myrec[k * 32 + lane] = s;
             __threadfence();
             __syncwarp();
+            int c_a = 0, c_b = 0, last = 0;
             if (lane == 0) {
-                const int c_a = cta_of_unit((long long)rb * a.upr, a.total_units, nctas);
-                const int c_b = cta_of_unit((long long)(rb + 1) * a.upr - 1, a.total_units, nctas);
-                const int prev = atomicAdd(a.counters + rb, 1);
-                flags[k] = (prev == c_b - c_a) ? 1 : 0;
+                c_a = part_of(r_b * G, a.part_q, a.part_r);
+                c_b = part_of((r_b + 1) * G - 1, a.part_q, a.part_r);
+                const int prev = atomicAdd(a.counters + r_b, 1);
+                last = (prev == c_b - c_a) ? 1 : 0;
             }
-            __syncwarp();
-            if (flags[k]) {                       // last contributor: finish the row block
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
                 __threadfence();
-                const int c_a = cta_of_unit((long long)rb * a.upr, a.total_units, nctas);
-                const int c_b = cta_of_unit((long long)(rb + 1) * a.upr - 1, a.total_units, nctas);
+                c_a = __shfl_sync(0xffffffffu, c_a, 0);
+                c_b = __shfl_sync(0xffffffffu, c_b, 0);
                 float tot = 0.f;
                 for (int c = c_a; c <= c_b; c++) {
-                    const int c_first_rb = (int)(cta_start(c, a.total_units, nctas) / a.upr);
-                    const int kk = (rb == c_first_rb) ? 0 : 1;
-                    tot += __ldcg(a.ws + ((size_t)c * 2 + kk) * 32 + lane);
+                    // record 0 of a CTA belongs to its first row block, record 1 to its last
+                    const int c_rb = (int)((unsigned)part_start(c, a.part_q, a.part_r) / (unsigned)G);
+                    tot += __ldcg(a.ws + (size_t)c * 64 + ((r_b == c_rb) ? 0 : 32) + lane);
                 }
-                const int r = rb * 16 + row;
                 if (r < a.rows && b < nb) a.y[(size_t)b * a.rows + r] = __float2half_rn(tot * oscale);
-                if (lane == 0) a.counters[rb] = 0;
+                if (lane == 0) a.counters[r_b] = 0;
             }
         }
     }
+    PHASE(6);
 }
 
 // ---------------------------------------------------------------------------
@@ -516,14 +680,22 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.rows = rows;
     a.cols = cols;
     a.groups = cols / kGroup;
-    a.upr = (a.groups + kUnitGroups - 1) / kUnitGroups;
-    a.nrb = (rows + 15) / 16;
     a.batch = batch;
-    a.total_units = (long long)a.nrb * a.upr;
-    if (a.nrb > kMaxRowBlocks) return fail(TLLM_ERR_SHAPE, "rows=%d exceeds %d", rows, kMaxRowBlocks * 16);
+    const int nrb = (rows + 15) / 16;
+    if (nrb > kMaxRowBlocks) return fail(TLLM_ERR_SHAPE, "rows=%d exceeds %d", rows, kMaxRowBlocks * 16);
+    if ((long long)nrb * a.groups >= (1ll << 26))
+        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: more than 2^26 tiles", rows, cols);
+    const int tiles = nrb * a.groups;
     int grid = s->sms < kMaxCtas ? s->sms : kMaxCtas;
-    if (a.total_units < grid) grid = (int)a.total_units;
-    a.max_units_per_cta = (int)((a.total_units + grid - 1) / grid) + 1;
+    // Whole row blocks per CTA when that keeps the SMs at least 80 % evenly loaded: no
+    // row block then spans two CTAs and the cross-CTA combine never runs.  Otherwise
+    // split at tile granularity (K is split across CTAs).
+    const int per_cta_rb = (nrb + grid - 1) / grid;
+    a.aligned = (nrb >= grid && (double)nrb / ((double)per_cta_rb * grid) >= 0.8) ? 1 : 0;
+    const int items = a.aligned ? nrb : tiles;
+    if (items < grid) grid = items;
+    a.part_q = items / grid;
+    a.part_r = items % grid;
     unsigned ticket;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -531,23 +703,25 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     }
     a.ws = s->ws + (size_t)ticket * kMaxCtas * 64;
     a.counters = s->counters + (size_t)ticket * kMaxRowBlocks;
-    // shared memory: activations | xfac | partials | ring | flags
+    a.err = s->misc + 1;
+    // shared memory: activations | xfac | partial sums | rings | mbarriers
     size_t xbytes;
     if (mode == kI8) xbytes = (size_t)cols;
-    else xbytes = (size_t)a.groups * 4 * ((mode == kF16B2) ? 32 : 16) * 8;
+    else xbytes = (size_t)a.groups * 2 * ((mode == kF16B2) ? 32 : 16) * 16;
     size_t off = (xbytes + 15) & ~(size_t)15;
     a.off_xfac = (int)off;
     off += (size_t)2 * a.groups * sizeof(float);
     off = (off + 15) & ~(size_t)15;
     a.off_part = (int)off;
-    off += (size_t)a.max_units_per_cta * 32 * sizeof(float);
+    const int max_rb_per_cta = a.aligned ? (a.part_q + 1) : ((a.part_q + 1 + a.groups - 1) / a.groups + 1);
+    off += (size_t)(max_rb_per_cta + kWarps) * 32 * sizeof(float);
     off = (off + 15) & ~(size_t)15;
     a.off_ring = (int)off;
-    off += (size_t)kWarps * kRing * kUnitBytes;
-    a.off_flags = (int)off;
-    off += 16;
+    off += (size_t)kWarps * kRing * kSlotBytes;
+    a.off_bar = (int)off;
+    off += (size_t)kWarps * kRing * 8;
     if (off > 227 * 1024)
-        return fail(TLLM_ERR_SHAPE, "cols=%d needs %zu bytes of shared memory (limit 232448)", cols, off);
+        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d needs %zu bytes of shared memory (limit 232448)", rows, cols, off);
     switch (mode) {
         case kF16B1: return launch_mode<kF16B1>(a, grid, off, stream, s);
         case kF16B2: return launch_mode<kF16B2>(a, grid, off, stream, s);
@@ -602,12 +776,37 @@ int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint3
     return check_launch("unpack");
 }
 
+// Synchronises `stream`, then reports and clears the device error flag.
+int device_error_check(cudaStream_t stream)
+{
+    DeviceScratch* s = nullptr;
+    int st = get_scratch(&s);
+    if (st) return st;
+    if (cudaStreamSynchronize(stream) != cudaSuccess)
+        return fail(TLLM_ERR_LAUNCH, "stream sync: %s", cudaGetErrorString(cudaGetLastError()));
+    int flag = 0;
+    if (cudaMemcpy(&flag, s->misc + 1, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return fail(TLLM_ERR_LAUNCH, "error flag read: %s", cudaGetErrorString(cudaGetLastError()));
+    if (flag != 0) {
+        cudaMemset(s->misc + 1, 0, sizeof(int));
+        return fail(flag, "a kernel reported status %d (bounded wait expired)", flag);
+    }
+    return TLLM_OK;
+}
+
 int weight_register(const void* nz, const uint8_t* packed, int rows, int cols)
 {
     std::lock_guard<std::mutex> lk(g_reg_mu);
     g_registry[nz] = Registered{packed, rows, cols};
     return TLLM_OK;
 }
+
+#ifdef TLLM_PROFILE_PHASES
+extern "C" int tllm_b200_debug_phases(unsigned long long* host_out, int n)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, g_phase_ns, sizeof(unsigned long long) * n);
+}
+#endif
 
 int weight_unregister(const void* nz)
 {

@@ -148,3 +148,8 @@ def ternary_gemv_int8_packed(w: PreparedWeight, input_int8, input_scale: float, 
     _lib.check(_lib.lib().tllm_b200_gemv_int8_packed(w.packed.data_ptr(), _chk(input_int8, torch.int8, "input_int8"),
                                                      float(input_scale), _chk(output, torch.float16, "output"),
                                                      w.rows, w.cols, _stream()))
+
+
+def check_device_errors() -> None:
+    """Synchronises the current stream and raises if a kernel's bounded wait expired."""
+    _lib.check(_lib.lib().tllm_b200_check_device_errors(_stream()))

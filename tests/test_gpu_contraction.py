@@ -227,7 +227,7 @@ def test_against_reference_cuda_kernels():
     # ulp: allow values that sit on a rounding boundary to differ by one step
     d = (q.cpu().numpy().astype(np.int32) - q_ref.cpu().numpy().astype(np.int32))
     assert np.abs(d).max() <= 1 and (d != 0).mean() < 1e-3
-    assert abs(s.item() - s_ref.item()) <= 1e-7 * abs(s.item())
+    assert abs(s.item() - s_ref.item()) <= 2.4e-7 * abs(s.item())   # fast-math division: 1-2 ulp
     # GEMM against the reference GEMM kernel
     m = 8
     a = np.random.default_rng(3).standard_normal((m, k)).astype(np.float16)
