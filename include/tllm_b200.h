@@ -158,6 +158,15 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
                                void* y, int rows, int cols, void* stream);
 
 /*
+ * Prefill GEMM on prepared weights: C[M,N] = A[M,K] . W^T, same contract as
+ * tllm_b200_gemm.  M > TLLM_MAX_BATCH runs the tcgen05 tensor-core kernel (weights
+ * expanded to exact FP16 {-s,0,+s} in tensor memory, FP32 accumulation in TMEM);
+ * smaller M runs the batched GEMV.  tllm_b200_gemm reaches the same kernels when
+ * the weight pointer has been registered.
+ */
+int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int N, int K, void* stream);
+
+/*
  * Device-side waits in the kernels are bounded; one that expires sets a flag on
  * the device and the kernel returns early (its output is then invalid).  This
  * call SYNCHRONISES `stream`, returns TLLM_ERR_TIMEOUT if the flag was set since

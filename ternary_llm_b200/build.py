@@ -39,7 +39,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
     cmd = ["nvcc"] + NVCC_FLAGS + ["-I" + os.path.join(ROOT, "include"),
-                                   "-I" + os.path.join(PKG, "csrc"), "-o", LIB] + sources() + ["-lcuda"]
+                                   "-I" + os.path.join(PKG, "csrc"), "-o", LIB] + sources()
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

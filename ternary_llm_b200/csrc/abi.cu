@@ -147,6 +147,8 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B, 
     if ((st = check_device())) return st;
     // Token blocks of at most kMaxBatch rows, each one pass over the weights.
     const uint8_t* packed = lookup_packed(nz_B, N, K);
+    if (packed && M > kMaxBatch && gemm_tcgen05_supported(M, N, K))
+        return launch_gemm_tcgen05((const half*)A, packed, (half*)C, M, N, K, (cudaStream_t)stream);
     for (int m0 = 0; m0 < M; m0 += kMaxBatch) {
         const int b = (M - m0 < kMaxBatch) ? (M - m0) : kMaxBatch;
         if (packed) {
@@ -229,6 +231,20 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* xq, float input
     int st = check_packed_call(packed, xq, y, rows, cols);
     if (st) return st;
     return launch_gemv_int8_packed((const uint8_t*)packed, xq, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
+}
+
+int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int N, int K, void* stream)
+{
+    if (!A || !packed || !C) return fail(TLLM_ERR_NULL, "null pointer");
+    if (M < 1 || N < 1 || K < kGroup || K % kGroup)
+        return fail(TLLM_ERR_SHAPE, "M=%d N=%d K=%d: need M,N >= 1 and K a positive multiple of 128", M, N, K);
+    if (misaligned(A, 16) || misaligned(packed, 16)) return fail(TLLM_ERR_ALIGN, "A and packed must be 16-byte aligned");
+    if (misaligned(C, 2)) return fail(TLLM_ERR_ALIGN, "C must be 2-byte aligned");
+    int st = check_device();
+    if (st) return st;
+    if (M <= kMaxBatch)
+        return launch_gemv_packed((const uint8_t*)packed, (const half*)A, (half*)C, M, N, K, (cudaStream_t)stream);
+    return launch_gemm_tcgen05((const half*)A, (const uint8_t*)packed, (half*)C, M, N, K, (cudaStream_t)stream);
 }
 
 int tllm_b200_check_device_errors(void* stream)

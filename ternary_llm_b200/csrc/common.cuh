@@ -42,6 +42,10 @@ int weight_register(const void* nz, const uint8_t* packed, int rows, int cols);
 int weight_unregister(const void* nz);
 int device_error_check(cudaStream_t stream);
 
+// tcgen05 prefill GEMM on prepared weights (gemm_tcgen05.cu).
+bool gemm_tcgen05_supported(int M, int N, int K);
+int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, int N, int K, cudaStream_t stream);
+
 // ---- small device helpers --------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v)
 {

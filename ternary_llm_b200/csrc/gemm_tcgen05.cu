@@ -1,0 +1,403 @@
+// Prefill GEMM  C[M,N] = A[M,K] . W^T  on the 5th-generation tensor cores (sm_100a).
+//
+// W is ternary with one FP16 scale per 128 weights along K.  The product
+// scale * t is exactly representable in FP16, so the weight operand is expanded to
+// FP16 {-s, 0, +s} and a plain FP16 x FP16 -> FP32 contraction over the whole K
+// gives the reference result with nothing but FP32 accumulation rounding.
+//
+// One CTA computes a tile of 128 output features x 256 tokens:
+//   * the weight tile is the MMA's A operand and lives in TENSOR MEMORY: four
+//     expander warps (one thread per feature row = one TMEM lane) read the row's
+//     packed 2-bit codes (packed_layout.cuh) straight from global/L2, expand 128
+//     weights per stage with PRMT (codes -> FP16 high bytes, four weights per
+//     instruction) and one HMUL2 by the group scale per weight pair, and write them
+//     with tcgen05.st.  The expanded weights never touch shared memory, which
+//     leaves its bandwidth to the activation operand;
+//   * the activation tile [256 tokens x 128 K] is the B operand in shared memory,
+//     brought by TMA (two 128-byte-swizzled boxes of 64 K per stage, 3 stages);
+//   * one thread issues tcgen05.mma (kind::f16, M=128, N=256, K=16; A from TMEM, B
+//     from a shared-memory descriptor) into a 128 x 256 FP32 accumulator in TMEM;
+//   * the expander warps then read the accumulator back with tcgen05.ld and store
+//     C (a TMEM lane is an output feature, so a warp writes 32 adjacent features
+//     of one token at a time).
+// TMEM: columns 0..255 accumulator, 256..383 two weight stages of 64 columns.
+// All mbarrier waits are bounded; a wait that gives up sets the device error flag
+// and every role falls through to the common exit, where TMEM is released.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "packed_layout.cuh"
+
+namespace tllm {
+
+namespace gemm {
+
+constexpr int kTileN = 128;          // output features per CTA (MMA M, TMEM lanes)
+constexpr int kTileM = 256;          // tokens per CTA (MMA N)
+constexpr int kStageK = 128;         // K per pipeline stage = one scale group
+constexpr int kBStages = 3;          // activation stages in shared memory
+constexpr int kAStages = 2;          // weight stages in tensor memory
+constexpr int kBoxK = 64;            // TMA box inner extent (128 bytes of FP16)
+constexpr int kBoxBytes = kTileM * kBoxK * 2;          // 32 KB
+constexpr int kStageBytes = 2 * kBoxBytes;             // 64 KB
+constexpr int kThreads = 256;
+constexpr int kAccCols = kTileM;     // 256 FP32 accumulator columns
+constexpr int kAColsPerStage = kStageK / 2;            // 64 columns of FP16 pairs
+constexpr int kTmemCols = 512;
+
+// PRMT tables: pair code -> FP16 high byte (+1 -> 0x3C, -1 -> 0xBC, 0 -> 0x00).
+// index:            0     1     2     3     4     5     6     7
+// weight a:        +1    +1    +1     0     0    -1    -1    -1
+// weight b:        +1     0    -1    +1    -1    +1     0    -1
+constexpr uint32_t kHiA_lo = 0x003C3C3Cu, kHiA_hi = 0xBCBCBC00u;
+constexpr uint32_t kHiB_lo = 0x3CBC003Cu, kHiB_hi = 0xBC003CBCu;
+
+struct Args {
+    const uint8_t* packed;     // packed weights [ceil(N/16)][K/128] tiles
+    half* C;                   // [M, N]
+    int M, N, K, groups;       // groups = K / 128
+    int nrb;                   // ceil(N / 16)
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; false = gave up (also when another role already reported an error).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (int i = 0; i < (1 << 22); i++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 1023) == 1023 && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128
+// bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                                 // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                                 // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                                 // layout: 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: FP16 x FP16 -> FP32, both operands K-major.
+__device__ __forceinline__ uint32_t make_idesc()
+{
+    uint32_t d = 0;
+    d |= 1u << 4;                          // D format F32
+    d |= 0u << 7;                          // A format F16
+    d |= 0u << 10;                         // B format F16
+    d |= (uint32_t)(kTileM >> 3) << 17;    // N
+    d |= (uint32_t)(kTileN >> 4) << 24;    // M
+    return d;
+}
+
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t lo, uint32_t hi, uint32_t sel)
+{
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(lo), "r"(hi), "r"(sel));
+    return r;
+}
+
+// Four FP16 high bytes -> two registers of FP16 pairs {-s,0,+s}.
+__device__ __forceinline__ void expand4(uint32_t hb, __half2 s2, uint32_t& r01, uint32_t& r23)
+{
+    const uint32_t u01 = __byte_perm(hb, 0u, 0x1404), u23 = __byte_perm(hb, 0u, 0x3424);
+    const __half2 v01 = __hmul2(*reinterpret_cast<const __half2*>(&u01), s2);
+    const __half2 v23 = __hmul2(*reinterpret_cast<const __half2*>(&u23), s2);
+    r01 = *reinterpret_cast<const uint32_t*>(&v01);
+    r23 = *reinterpret_cast<const uint32_t*>(&v23);
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the 128-byte swizzle atoms
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * kBStages + 2 * kAStages + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kTileN;          // first output feature of the tile
+    const int m0 = blockIdx.y * kTileM;          // first token of the tile
+    const int nstages = a.groups;                // one scale group per stage
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_b = [&](int s) { return bar0 + 8u * s; };
+    auto empty_b = [&](int s) { return bar0 + 8u * (kBStages + s); };
+    auto full_a = [&](int s) { return bar0 + 8u * (2 * kBStages + s); };
+    auto empty_a = [&](int s) { return bar0 + 8u * (2 * kBStages + kAStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * kBStages + 2 * kAStages);
+
+    if (tid == 0) {
+        for (int s = 0; s < kBStages; s++) {
+            mbar_init(full_b(s), 1);
+            mbar_init(empty_b(s), 1);
+        }
+        for (int s = 0; s < kAStages; s++) {
+            mbar_init(full_a(s), 128);
+            mbar_init(empty_a(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {       // one warp allocates all 512 TMEM columns of this SM
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base_slot;
+    volatile int* abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activations ----------------
+        if (lane == 0) {
+            for (int it = 0; it < nstages; it++) {
+                const int s = it % kBStages;
+                if (!mbar_wait(empty_b(s), ((it / kBStages) & 1) ^ 1, abortp)) { abort_flag = 1; break; }
+                mbar_expect_tx(full_b(s), kStageBytes);
+                const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes);
+                tma_load_2d(dst, &map_a, it * kStageK, m0, full_b(s));
+                tma_load_2d(dst + kBoxBytes, &map_a, it * kStageK + kBoxK, m0, full_b(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc();
+            for (int it = 0; it < nstages; it++) {
+                const int sb = it % kBStages, sa = it % kAStages;
+                if (!mbar_wait(full_b(sb), (it / kBStages) & 1, abortp) ||
+                    !mbar_wait(full_a(sa), (it / kAStages) & 1, abortp)) { abort_flag = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t bsm = smem_u32(smem + (size_t)sb * kStageBytes);
+                const uint32_t a_t = tmem + kAccCols + sa * kAColsPerStage;
+#pragma unroll
+                for (int k = 0; k < kStageK / 16; k++) {
+                    // K step of 16: 32 bytes inside the 128-byte swizzled row; second box after 64 K
+                    const uint64_t bd = make_b_desc(bsm + (k >> 2) * kBoxBytes + (k & 3) * 32);
+                    mma_ts(tmem, a_t + k * 8, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(empty_b(sb));
+                mma_commit(empty_a(sa));
+            }
+            mma_commit(acc_full);
+        }
+    } else if (warp >= 4) {
+        // ---------------- weight expanders, then epilogue ----------------
+        const int row = tid - 128;                       // feature row inside the tile = TMEM lane
+        const int n = n0 + row;
+        const int rb = n >> 4, r16 = n & 15;
+        const bool row_valid = rb < a.nrb;               // rows past the matrix expand to zeros
+        const uint8_t* tile0 = a.packed + (size_t)(row_valid ? rb : 0) * a.groups * kTileBytes;
+        const int spos = (r16 < 8) ? 2 * r16 : 2 * (r16 - 8) + 1;
+        const uint32_t lane_base = tmem + ((uint32_t)(row & ~31) << 16);   // this warp's 32 TMEM lanes
+
+        uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
+        half sc = __float2half(0.f);
+        if (row_valid) {
+            c0 = __ldg(reinterpret_cast<const uint4*>(tile0 + r16 * 32));
+            c1 = __ldg(reinterpret_cast<const uint4*>(tile0 + r16 * 32 + 16));
+            sc = __ldg(reinterpret_cast<const half*>(tile0 + kTileCodeBytes) + spos);
+        }
+        bool ok = true;
+        for (int it = 0; it < nstages; it++) {
+            const int sa = it % kAStages;
+            // codes of lanes t = 0..3 of this row: words {step 0|1, step 2|3}
+            const uint32_t w[4][2] = {{c0.x, c0.y}, {c0.z, c0.w}, {c1.x, c1.y}, {c1.z, c1.w}};
+            const __half2 s2 = __half2half2(sc);
+            if (it + 1 < nstages && row_valid) {          // prefetch the next group's codes and scale
+                const uint8_t* tp = tile0 + (size_t)(it + 1) * kTileBytes;
+                c0 = __ldg(reinterpret_cast<const uint4*>(tp + r16 * 32));
+                c1 = __ldg(reinterpret_cast<const uint4*>(tp + r16 * 32 + 16));
+                sc = __ldg(reinterpret_cast<const half*>(tp + kTileCodeBytes) + spos);
+            }
+            if (!mbar_wait(empty_a(sa), ((it / kAStages) & 1) ^ 1, abortp)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_t = lane_base + kAccCols + sa * kAColsPerStage;
+#pragma unroll
+            for (int m = 0; m < 4; m++) {                 // 32 K per step -> 16 columns
+                uint32_t r[16];
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const uint32_t word = w[t][m >> 1];
+                    const uint32_t sel = (m & 1) ? (word >> 16) : word;
+                    // weights at K offsets 4t..4t+3 (columns 2t, 2t+1) and 16+4t.. (columns 8+2t, 9+2t)
+                    expand4(prmt(kHiA_lo, kHiA_hi, sel), s2, r[2 * t], r[2 * t + 1]);
+                    expand4(prmt(kHiB_lo, kHiB_hi, sel), s2, r[8 + 2 * t], r[9 + 2 * t]);
+                }
+                tmem_st16(a_t + m * 16, r);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(full_a(sa));
+        }
+        if (!ok) abort_flag = 1;
+
+        // ---------------- epilogue: accumulator -> C ----------------
+        if (ok && mbar_wait(acc_full, 0, abortp)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int cchunk = 0; cchunk < kTileM / 32; cchunk++) {
+                if (m0 + cchunk * 32 >= a.M) break;       // uniform: no tokens left in this chunk
+                uint32_t v[32];
+                tmem_ld32(lane_base + cchunk * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < a.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int m = m0 + cchunk * 32 + j;
+                        if (m < a.M) a.C[(size_t)m * a.N + n] = __float2half_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+        } else {
+            abort_flag = 1;
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (abort_flag && tid == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point query, so that the
+// library has no link-time dependency on libcuda (it must load on machines without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+}  // namespace gemm
+
+int* device_error_flag();   // gemv_mma.cu
+
+bool gemm_tcgen05_supported(int M, int N, int K)
+{
+    (void)N;
+    return M >= 1 && K >= gemm::kStageK && K % gemm::kStageK == 0;
+}
+
+// A: half [M,K] row-major (16-byte aligned), packed: prepared weights of [N,K], C: half [M,N].
+int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, int N, int K, cudaStream_t stream)
+{
+    using namespace gemm;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(TLLM_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kBoxK, (cuuint32_t)kTileM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TLLM_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
+
+    int* err = device_error_flag();
+    if (!err) return fail(TLLM_ERR_LAUNCH, "device scratch unavailable");
+    Args a;
+    a.packed = packed;
+    a.C = C;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.groups = K / kStageK;
+    a.nrb = (N + 15) / 16;
+    a.err = err;
+    const size_t smem = (size_t)kBStages * kStageBytes + 1024;
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr[dev]) {
+        cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr[dev] = true;
+    }
+    const dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
+    gemm_kernel<<<grid, kThreads, smem, stream>>>(map, a);
+    return check_launch("gemm_tcgen05");
+}
+
+}  // namespace tllm

@@ -776,6 +776,14 @@ int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint3
     return check_launch("unpack");
 }
 
+// Device error flag of the current device (nullptr if the scratch cannot be set up).
+int* device_error_flag()
+{
+    DeviceScratch* s = nullptr;
+    if (get_scratch(&s) != TLLM_OK) return nullptr;
+    return s->misc + 1;
+}
+
 // Synchronises `stream`, then reports and clears the device error flag.
 int device_error_check(cudaStream_t stream)
 {

@@ -150,6 +150,12 @@ def ternary_gemv_int8_packed(w: PreparedWeight, input_int8, input_scale: float, 
                                                      w.rows, w.cols, _stream()))
 
 
+def ternary_gemm_packed(A, w: PreparedWeight, C, M: int) -> None:
+    """C[M,N] = A[M,K] . W^T on prepared weights (tcgen05 kernel for M > 16)."""
+    _lib.check(_lib.lib().tllm_b200_gemm_packed(_chk(A, torch.float16, "A"), w.packed.data_ptr(),
+                                                _chk(C, torch.float16, "C"), M, w.rows, w.cols, _stream()))
+
+
 def check_device_errors() -> None:
     """Synchronises the current stream and raises if a kernel's bounded wait expired."""
     _lib.check(_lib.lib().tllm_b200_check_device_errors(_stream()))
