@@ -158,6 +158,23 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
                                void* y, int rows, int cols, void* stream);
 
 /*
+ * tllm_b200_gemv_packed for one FP16 vector, for callers that cannot let a library
+ * allocate device memory (a server that owns all of HBM through its own arena, a
+ * real-time loop, a host that audits allocations up front).  It has no counterpart
+ * in the reference.  Nothing is allocated, by this call or any routine it uses: the
+ * split-K scratch is a fixed 82 KB array inside the library image, present on every
+ * GPU that loads the library until the process exits.
+ * Limits: rows <= 65536 (TLLM_ERR_SIZE beyond), cols as for tllm_b200_gemv_packed.
+ * The first call on a device resolves the array's device address and configures the
+ * kernel; make that first call before any stream capture.  All calls share the one
+ * array and it keeps the last call's contents (the arrival counters are cleared on
+ * `stream` before each launch): calls whose kernels overlap on the GPU, for example
+ * from two streams, race with each other -- serialise them.
+ */
+int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y,
+                                  int rows, int cols, void* stream);
+
+/*
  * Prefill GEMM on prepared weights: C[M,N] = A[M,K] . W^T, same contract as
  * tllm_b200_gemm.  M > TLLM_MAX_BATCH runs the tcgen05 tensor-core kernel (weights
  * expanded to exact FP16 {-s,0,+s} in tensor memory, FP32 accumulation in TMEM);

@@ -233,6 +233,14 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* xq, float input
     return launch_gemv_int8_packed((const uint8_t*)packed, xq, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
 }
 
+int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y, int rows, int cols, void* stream)
+{
+    int st = check_packed_call(packed, x, y, rows, cols);
+    if (st) return st;
+    return launch_gemv_packed_noalloc((const uint8_t*)packed, (const half*)x, (half*)y, rows, cols,
+                                      (cudaStream_t)stream);
+}
+
 int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int N, int K, void* stream)
 {
     if (!A || !packed || !C) return fail(TLLM_ERR_NULL, "null pointer");

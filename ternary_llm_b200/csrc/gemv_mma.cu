@@ -742,6 +742,103 @@ int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch,
     return TLLM_OK;
 }
 
+// ---------------------------------------------------------------------------
+// GEMV for callers that must not allocate
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot let it call cudaMalloc: an inference server that
+// has handed all device memory to its own arena, code running inside a region where
+// the allocator is forbidden (a real-time loop, a stream capture), or a process whose
+// memory budget is audited up front.  For them the split-K combine scratch of the
+// GEMV lives in this fixed array instead of a lazily allocated buffer.  Every GPU that
+// loads the library carries these 82 KB until the process exits.
+//   [0, 65536)        partial-sum records, kMaxCtas x 64 floats
+//   [65536, 81920)    arrival counters, kNoAllocMaxRowBlocks ints
+//   [81920, 81924)    device error flag
+constexpr int kNoAllocMaxRows = 65536;
+constexpr int kNoAllocMaxRowBlocks = kNoAllocMaxRows / 16;
+constexpr size_t kNoAllocWsBytes = (size_t)kMaxCtas * 64 * sizeof(float);
+constexpr size_t kNoAllocCounterBytes = (size_t)kNoAllocMaxRowBlocks * sizeof(int);
+constexpr size_t kNoAllocBytes = kNoAllocWsBytes + kNoAllocCounterBytes + 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+struct NoAllocDevice {
+    unsigned char* base = nullptr;   // device address of g_noalloc_scratch on this device
+    int sms = 0;
+};
+static NoAllocDevice g_noalloc[64];
+
+// One FP16 vector, prepared weights, no allocation of any kind.  The first call on a
+// device looks up the device address of the scratch array (cudaGetSymbolAddress, with
+// that device current) and raises the kernel's shared-memory limit; make that first
+// call outside any stream capture.  All calls share the one scratch array, which
+// keeps what the previous call left: the counters are cleared on `stream` before each
+// launch, and two calls whose kernels overlap on the GPU (different streams) race.
+int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
+                               cudaStream_t stream)
+{
+    if (rows > kNoAllocMaxRows)
+        return fail(TLLM_ERR_SIZE, "rows=%d exceeds the no-allocation variant's maximum of %d", rows, kNoAllocMaxRows);
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(TLLM_ERR_DEVICE, "no usable current device");
+    NoAllocDevice& nd = g_noalloc[dev];
+    if (!nd.base) {
+        // In host code the array's name is only a handle; the kernel needs the address
+        // the array has on THIS device.
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail(TLLM_ERR_LAUNCH, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+        }
+        if (cudaDeviceGetAttribute(&nd.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || nd.sms < 1)
+            return fail(TLLM_ERR_DEVICE, "cannot read the SM count of device %d", dev);
+        nd.base = static_cast<unsigned char*>(p);
+    }
+    GemvArgs a = {};
+    a.packed = packed;
+    a.x = x;
+    a.y = y;
+    a.in_scale = 1.0f;
+    a.rows = rows;
+    a.cols = cols;
+    a.groups = cols / kGroup;
+    a.batch = 1;
+    const int nrb = (rows + 15) / 16;
+    if ((long long)nrb * a.groups >= (1ll << 26))
+        return fail(TLLM_ERR_SIZE, "rows=%d cols=%d: more than 2^26 tiles", rows, cols);
+    const int tiles = nrb * a.groups;
+    int grid = nd.sms < kMaxCtas ? nd.sms : kMaxCtas;
+    const int per_cta_rb = (nrb + grid - 1) / grid;
+    a.aligned = (nrb >= grid && (double)nrb / ((double)per_cta_rb * grid) >= 0.8) ? 1 : 0;
+    const int items = a.aligned ? nrb : tiles;
+    if (items < grid) grid = items;
+    a.part_q = items / grid;
+    a.part_r = items % grid;
+    a.ws = reinterpret_cast<float*>(nd.base);
+    a.counters = reinterpret_cast<int*>(nd.base + kNoAllocWsBytes);
+    a.err = reinterpret_cast<int*>(nd.base + kNoAllocWsBytes + kNoAllocCounterBytes);
+    size_t off = ((size_t)a.groups * 2 * 16 * 16 + 15) & ~(size_t)15;
+    a.off_xfac = (int)off;
+    off += (size_t)2 * a.groups * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_part = (int)off;
+    const int max_rb_per_cta = a.aligned ? (a.part_q + 1) : ((a.part_q + 1 + a.groups - 1) / a.groups + 1);
+    off += (size_t)(max_rb_per_cta + kWarps) * 32 * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_ring = (int)off;
+    off += (size_t)kWarps * kRing * kSlotBytes;
+    a.off_bar = (int)off;
+    off += (size_t)kWarps * kRing * 8;
+    if (off > 227 * 1024)
+        return fail(TLLM_ERR_SIZE, "cols=%d needs %zu bytes of shared memory (limit 232448)", cols, off);
+    // the counters must start at zero; a call that was cut short may have left some set
+    if (cudaMemsetAsync(a.counters, 0, (size_t)nrb * sizeof(int), stream) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLLM_ERR_LAUNCH, "clearing the scratch counters failed");
+    }
+    return launch_mode<kF16B1>(a, grid, off, stream, nullptr);
+}
+
 int launch_gemv_int8_packed(const uint8_t* packed, const int8_t* xq, float in_scale, half* y, int rows,
                             int cols, cudaStream_t stream)
 {
