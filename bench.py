@@ -60,6 +60,14 @@ def measured_peak_hbm():
     return 6650.0, "fallback"
 
 
+def measured_peak_bf16():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -174,6 +182,146 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------
+# GPU arm, N > 1: tensor-parallel LLaMA-70B-shape layer stack
+# --------------------------------------------------------------------------
+H70, Q70, KV70, I70, LAYERS_70B = 8192, 8192, 1024, 28672, 80
+METRIC_TP = "ternary_gemv_hbm_throughput_llama70b_shapes_tp_batch1"
+
+
+def tp_shapes(tp: int):
+    """Per-rank (name, rows, cols) of one layer: q/k/v/gate/up are column-parallel
+    (rows split), o/down are row-parallel (cols split on 128-aligned boundaries)."""
+    assert Q70 % (16 * tp) == 0 and KV70 % (16 * tp) == 0 and I70 % (128 * tp) == 0 and H70 % (128 * tp) == 0
+    return [("q", Q70 // tp, H70), ("k", KV70 // tp, H70), ("v", KV70 // tp, H70), ("o", H70, Q70 // tp),
+            ("gate", I70 // tp, H70), ("up", I70 // tp, H70), ("down", H70, I70 // tp)]
+
+
+def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
+    shapes = tp_shapes(world)
+    full = [("q", Q70, H70), ("k", KV70, H70), ("v", KV70, H70), ("o", H70, Q70), ("gate", I70, H70),
+            ("up", I70, H70), ("down", H70, I70)]
+    step_bytes = LAYERS_70B * sum(gemv_bytes(n, k) for _, n, k in full)
+    layers = []
+    for li in range(LAYERS_70B):
+        mats = []
+        for mi, (_, n, k) in enumerate(shapes):
+            nz, sg, sc = synth.random_ternary_weight(n, k, seed=1_000_000 * rank + 100 * li + mi, device=dev)
+            mats.append(tl.PreparedWeight(nz, sg, sc, n, k, register=False, keep_source=False))
+            del nz, sg, sc
+        layers.append(mats)
+    gen = torch.Generator(device=dev).manual_seed(99)
+    x_h = torch.randn(H70, generator=gen, device=dev).half()            # layer input (replicated)
+    x_attn = torch.randn(Q70 // world, generator=gen, device=dev).half()  # local slice of the attention output
+    x_ffn = torch.randn(I70 // world, generator=gen, device=dev).half()   # local slice of the SwiGLU output
+    yq = torch.zeros(Q70 // world, dtype=torch.float16, device=dev)
+    yk = torch.zeros(KV70 // world, dtype=torch.float16, device=dev)
+    yv = torch.zeros(KV70 // world, dtype=torch.float16, device=dev)
+    yo = torch.zeros(H70, dtype=torch.float16, device=dev)
+    yg = torch.zeros(I70 // world, dtype=torch.float16, device=dev)
+    yu = torch.zeros(I70 // world, dtype=torch.float16, device=dev)
+    yd = torch.zeros(H70, dtype=torch.float16, device=dev)
+
+    def launch_step():
+        n = 0
+        for mats in layers:
+            q, k, v, o, g, u, d = mats
+            tl.ternary_gemv_packed(q, x_h, yq)
+            tl.ternary_gemv_packed(k, x_h, yk)
+            tl.ternary_gemv_packed(v, x_h, yv)
+            tl.ternary_gemv_packed(o, x_attn, yo)        # row-parallel: partial sums ...
+            dist.all_reduce(yo)                          # ... combined over NVLink
+            tl.ternary_gemv_packed(g, x_h, yg)
+            tl.ternary_gemv_packed(u, x_h, yu)
+            tl.ternary_gemv_packed(d, x_ffn, yd)
+            dist.all_reduce(yd)
+            n += 7
+        return n
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        launches = launch_step()
+        torch.cuda.synchronize()
+        graph, mode = None, "eager launches"
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                launch_step()
+            graph, mode = g, "CUDA graph replay of the whole step (NCCL all-reduce captured)"
+        except Exception as e:      # capture of the collective is not available: launch eagerly
+            mode = f"eager launches (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+
+        def step():
+            if graph is not None:
+                graph.replay()
+            else:
+                launch_step()
+
+        def barrier():
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clk:
+            e0.record(stream)
+            for _ in range(args.steps):
+                step()
+            e1.record(stream)
+            barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = clk.summary()
+        # end to end: the step's input vector comes from pinned host memory and the
+        # step's output vector goes back to it, inside the timed region
+        x_host = x_h.cpu().pin_memory()
+        y_host = torch.empty(H70, dtype=torch.float16).pin_memory()
+        for _ in range(2):
+            x_h.copy_(x_host, non_blocking=True)
+            step()
+            y_host.copy_(yd, non_blocking=True)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(args.steps):
+            x_h.copy_(x_host, non_blocking=True)
+            step()
+            y_host.copy_(yd, non_blocking=True)
+        f1.record(stream)
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+    tl.check_device_errors()
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = (float(v) for v in t.tolist())
+    if rank == 0:
+        peak, peak_kind = measured_peak_hbm()
+        value = step_bytes * args.steps / (ms * 1e-3) / 1e9
+        per_gpu_bytes = LAYERS_70B * sum(gemv_bytes(n, k) for _, n, k in shapes)
+        print(json.dumps({
+            "metric": METRIC_TP, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "s8 MMA (exact s32 group sums), f32 accumulate", "data": "synthetic",
+            "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, 80 layers), batch 1, decode-style pass",
+                       "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, NCCL all-reduce of the 8192-vector after o and after down (160 per step)",
+                       "gemv_per_step_per_gpu": launches, "bytes_per_step": step_bytes,
+                       "l2": f"{per_gpu_bytes/1e9:.2f} GB of distinct weights per GPU per step (> 126 MB L2), no flush needed",
+                       "launch": mode},
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "whole sharded step per GPU (GEMVs + all-reduces)"},
+            "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": 2 * H70 * world, "d2h_bytes_per_step": 2 * H70 * world,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches * args.steps, "clocks": clocks,
+        }))
+    dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
 def run_ours(args):
@@ -193,6 +341,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     tl.lib()   # fail loudly here if the shared library is missing
+    if world > 1:
+        return run_tp(args, torch, dist, tl, synth, rank, world, local, dev)
 
     # ---- weights: 32 layers x 7 distinct matrices, seeded, on the device ----
     layers, prepared = [], []
@@ -305,6 +455,30 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e, ms_roof = (float(v) for v in t.tolist())
 
+    # ---- prefill GEMM at the same shapes, M = 2048 (reported beside the headline) ----
+    gemm_rows = []
+    with torch.cuda.stream(stream):
+        m_tok = 2048
+        for name, mi in (("q/o", 0), ("k/v", 1), ("gate/up", 4), ("down", 6)):
+            _, n, k = SHAPES_8B[mi]
+            a_act = torch.randn(m_tok, k, device=dev).half()
+            c_out = torch.empty(m_tok, n, dtype=torch.float16, device=dev)
+            ws = [prepared[li * len(SHAPES_8B) + mi] for li in range(8)]     # 8 distinct matrices
+            for w in ws[:3]:
+                tl.ternary_gemm_packed(a_act, w, c_out, m_tok)
+            torch.cuda.synchronize()
+            g0, g1 = ev(), ev()
+            g0.record(stream)
+            for w in ws:
+                tl.ternary_gemm_packed(a_act, w, c_out, m_tok)
+            g1.record(stream)
+            torch.cuda.synchronize()
+            us = g0.elapsed_time(g1) * 1e3 / len(ws)
+            gemm_rows.append({"shape": name, "M": m_tok, "N": n, "K": k, "us": us,
+                              "tflops": 2.0 * m_tok * n * k / us / 1e6})
+            del a_act, c_out
+    tl.check_device_errors()
+
     if rank == 0:
         peak, peak_kind = measured_peak_hbm()
         total_bytes = STEP_BYTES * world
@@ -330,6 +504,9 @@ def run_ours(args):
                     "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
+            "prefill_gemm": {"kernel": "tcgen05 kind::f16, weights expanded to exact FP16 in tensor memory",
+                             "peak_tflops": measured_peak_bf16(), "peak_kind": "measured bf16 cuBLAS burst",
+                             "rows": gemm_rows},
         }
         if world == 1 and not args.no_cpu:
             v, dt, kind, what = cpu_layer_sample(reps=3, threads=os.cpu_count() or 1)

@@ -99,10 +99,15 @@ class PreparedWeight:
     reference-signature entry points (ternary_gemv ...) called with these source
     tensors use the packed copy, as the C++ engine integration does."""
 
-    def __init__(self, nonzero_masks, sign_masks, scales, rows: int, cols: int, register: bool = True):
+    def __init__(self, nonzero_masks, sign_masks, scales, rows: int, cols: int, register: bool = True,
+                 keep_source: bool = True):
         nz, sg, sc = _weights(nonzero_masks, sign_masks, scales)
         self.rows, self.cols = rows, cols
-        self.nonzero_masks, self.sign_masks, self.scales = nonzero_masks, sign_masks, scales
+        if register and not keep_source:
+            raise ValueError("registered weights are keyed by the source tensor and must keep it")
+        # the source tensors can be dropped when only the packed entry points are used
+        self.nonzero_masks, self.sign_masks, self.scales = (
+            (nonzero_masks, sign_masks, scales) if keep_source else (None, None, None))
         nbytes = packed_bytes(rows, cols)
         if nbytes == 0:
             raise ValueError(f"unsupported shape rows={rows} cols={cols}")
