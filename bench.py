@@ -80,7 +80,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -196,13 +196,20 @@ def tp_shapes(tp: int):
             ("gate", I70 // tp, H70), ("up", I70 // tp, H70), ("down", H70, I70 // tp)]
 
 
+def _log(rank, msg):
+    if rank == 0 and os.environ.get("TLLM_BENCH_VERBOSE"):
+        print(f"[bench {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
     shapes = tp_shapes(world)
+    n_layers = args.layers if args.layers > 0 else LAYERS_70B
     full = [("q", Q70, H70), ("k", KV70, H70), ("v", KV70, H70), ("o", H70, Q70), ("gate", I70, H70),
             ("up", I70, H70), ("down", H70, I70)]
-    step_bytes = LAYERS_70B * sum(gemv_bytes(n, k) for _, n, k in full)
+    step_bytes = n_layers * sum(gemv_bytes(n, k) for _, n, k in full)
     layers = []
-    for li in range(LAYERS_70B):
+    _log(rank, f"generating {n_layers} layers of tp{world} shards")
+    for li in range(n_layers):
         mats = []
         for mi, (_, n, k) in enumerate(shapes):
             nz, sg, sc = synth.random_ternary_weight(n, k, seed=1_000_000 * rank + 100 * li + mi, device=dev)
@@ -237,12 +244,20 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             n += 7
         return n
 
+    _log(rank, "weights ready; first eager step")
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         launches = launch_step()
         torch.cuda.synchronize()
+        _log(rank, "eager step done; capturing")
         graph, mode = None, "eager launches"
+        if args.no_graph:
+            raise_capture = True
+        else:
+            raise_capture = False
         try:
+            if raise_capture:
+                raise RuntimeError("graph disabled by --no-graph")
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
                 launch_step()
@@ -250,6 +265,8 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
         except Exception as e:      # capture of the collective is not available: launch eagerly
             mode = f"eager launches (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
+
+        _log(rank, f"launch mode: {mode}")
 
         def step():
             if graph is not None:
@@ -262,18 +279,27 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             dist.barrier()
             torch.cuda.synchronize()
 
-        for _ in range(args.warmup):
+        sampler = ClockSampler(local)
+        sampler.__enter__()          # samples from warm-up to the end of the timed regions
+        for _ in range(max(args.warmup, 3)):
             step()
+        t_load = time.perf_counter()
+        n_extra = torch.zeros(1, dtype=torch.int32, device=dev)
+        while True:                                   # keep the GPUs under load until clock samples exist
+            step()
+            torch.cuda.synchronize()
+            n_extra[0] = 1 if time.perf_counter() - t_load < 0.5 else 0
+            dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)   # all ranks leave the loop together
+            if int(n_extra.item()) == 0:
+                break
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local) as clk:
-            e0.record(stream)
-            for _ in range(args.steps):
-                step()
-            e1.record(stream)
-            barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
         ms = e0.elapsed_time(e1)
-        clocks = clk.summary()
         # end to end: the step's input vector comes from pinned host memory and the
         # step's output vector goes back to it, inside the timed region
         x_host = x_h.cpu().pin_memory()
@@ -292,6 +318,8 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
         f1.record(stream)
         barrier()
         ms_e2e = f0.elapsed_time(f1)
+        sampler.__exit__(None, None, None)
+        clocks = sampler.summary()
     tl.check_device_errors()
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -299,13 +327,13 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
     if rank == 0:
         peak, peak_kind = measured_peak_hbm()
         value = step_bytes * args.steps / (ms * 1e-3) / 1e9
-        per_gpu_bytes = LAYERS_70B * sum(gemv_bytes(n, k) for _, n, k in shapes)
+        per_gpu_bytes = n_layers * sum(gemv_bytes(n, k) for _, n, k in shapes)
         print(json.dumps({
             "metric": METRIC_TP, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 MMA (exact s32 group sums), f32 accumulate", "data": "synthetic",
-            "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, 80 layers), batch 1, decode-style pass",
+            "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, %d layers), batch 1, decode-style pass" % n_layers,
                        "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, NCCL all-reduce of the 8192-vector after o and after down (160 per step)",
                        "gemv_per_step_per_gpu": launches, "bytes_per_step": step_bytes,
                        "l2": f"{per_gpu_bytes/1e9:.2f} GB of distinct weights per GPU per step (> 126 MB L2), no flush needed",
@@ -317,8 +345,16 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
                     "h2d_bytes_per_step": 2 * H70 * world, "d2h_bytes_per_step": 2 * H70 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches * args.steps, "clocks": clocks,
-        }))
-    dist.destroy_process_group()
+        }), flush=True)
+    # Tearing down a process group whose collectives were captured in a CUDA graph can
+    # block forever: drop the graph, drain the device, meet at a barrier, then leave
+    # without the destructor path.
+    graph = None
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 # --------------------------------------------------------------------------
@@ -408,18 +444,22 @@ def run_ours(args):
         ev = lambda: torch.cuda.Event(enable_timing=True)
 
         # ---- device-resident timing -------------------------------------------
+        sampler = ClockSampler(local)
+        sampler.__enter__()          # samples from warm-up to the end of the timed regions
+        t_load = time.perf_counter()
         for _ in range(args.warmup):
             graph.replay()
+        while time.perf_counter() - t_load < 0.5:      # keep the GPU under load until samples exist
+            graph.replay()
+            torch.cuda.synchronize()
         barrier()
         e0, e1 = ev(), ev()
-        with ClockSampler(local) as clk:
-            e0.record(stream)
-            for _ in range(args.steps):
-                graph.replay()
-            e1.record(stream)
-            barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
         ms = e0.elapsed_time(e1)
-        clocks = clk.summary()
 
         # ---- end to end: pinned host -> device, run, device -> pinned host ----------
         for _ in range(max(1, args.warmup // 2)):
@@ -449,6 +489,8 @@ def run_ours(args):
         r1.record(stream)
         barrier()
         ms_roof = r0.elapsed_time(r1) / (reps * roof_launches)
+        sampler.__exit__(None, None, None)
+        clocks = sampler.summary()
 
     t = torch.tensor([ms, ms_e2e, ms_roof], dtype=torch.float64, device=dev)
     if world > 1:
@@ -520,10 +562,12 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=0, help="N>1 only: layer count override for quick checks (0 = the full 80)")
+    ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
