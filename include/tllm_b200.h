@@ -42,6 +42,7 @@ extern "C" {
 
 #define TLLM_GROUP_SIZE       128
 #define TLLM_MAX_BATCH        16
+#define TLLM_MAX_FUSED        4    /* matrices per tllm_b200_gemv_packed_multi call */
 
 /* Text for a status code; never NULL. */
 const char* tllm_b200_status_string(int status);
@@ -156,6 +157,17 @@ int tllm_b200_gemv_packed(const void* packed, const void* x, void* y,
                           int batch, int rows, int cols, void* stream);
 int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, float input_scale,
                                void* y, int rows, int cols, void* stream);
+
+/*
+ * y_i = W_i x for `count` (1..TLLM_MAX_FUSED) prepared matrices that share the FP16
+ * activation vector x and the column count -- q/k/v after the attention norm, gate/up
+ * after the FFN norm (the reference issues them as separate calls on the same input,
+ * src/transformer.cpp:206-222,271-283).  One launch streams all of them, so small
+ * matrices (k, v) no longer pay a launch each; results equal those of `count` calls
+ * of tllm_b200_gemv_packed up to the order of the FP32 additions over K.  packed, y, rows are HOST arrays of length count.
+ */
+int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows,
+                                int cols, const void* x, void* stream);
 
 /*
  * tllm_b200_gemv_packed for one FP16 vector, for callers that cannot let a library

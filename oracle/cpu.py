@@ -32,6 +32,13 @@ def build(ref_dir: str | None = "/root/reference") -> None:
     subprocess.check_call(["make", "-s", "-C", _HERE])
     if ref_dir and os.path.isdir(ref_dir):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_dir}"])
+        pkg_lib = os.path.join(os.path.dirname(_HERE), "ternary_llm_b200", "libtllm_b200.so")
+        if os.path.exists(pkg_lib):      # drop-in checks link against the built library
+            subprocess.check_call(["make", "-s", "-C", _HERE, "dropin", f"REF={ref_dir}"])
+
+
+DROPIN_TEST = os.path.join(_HERE, "_ref", "test_gemv_dropin")
+ENGINE_LINK = os.path.join(_HERE, "_ref", "engine_link")
 
 
 _port = None

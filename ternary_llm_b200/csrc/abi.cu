@@ -233,6 +233,19 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* xq, float input
     return launch_gemv_int8_packed((const uint8_t*)packed, xq, input_scale, (half*)y, rows, cols, (cudaStream_t)stream);
 }
 
+int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows, int cols,
+                                const void* x, void* stream)
+{
+    if (!packed || !y || !rows || !x) return fail(TLLM_ERR_NULL, "null pointer");
+    if (count < 1 || count > TLLM_MAX_FUSED) return fail(TLLM_ERR_BATCH, "count %d outside 1..%d", count, TLLM_MAX_FUSED);
+    for (int i = 0; i < count; i++) {
+        const int st = check_packed_call(packed[i], x, y[i], rows[i], cols);
+        if (st) return st;
+    }
+    return launch_gemv_packed_multi(count, (const uint8_t* const*)packed, (half* const*)y, rows, cols,
+                                    (const half*)x, (cudaStream_t)stream);
+}
+
 int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y, int rows, int cols, void* stream)
 {
     int st = check_packed_call(packed, x, y, rows, cols);

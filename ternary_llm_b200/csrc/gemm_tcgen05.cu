@@ -84,6 +84,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 // Bounded wait; false = gave up (also when another role already reported an error).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
+#pragma unroll 1
     for (int i = 0; i < (1 << 22); i++) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 1023) == 1023 && *abort_flag) return false;

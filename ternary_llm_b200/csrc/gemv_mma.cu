@@ -108,6 +108,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 // Bounded wait (about a second at most); false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
+#pragma unroll 1
     for (int i = 0; i < (1 << 22); i++)
         if (mbar_try(bar, parity)) return true;
     return false;
@@ -497,6 +498,240 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
 }
 
 // ---------------------------------------------------------------------------
+// Column-walk GEMV: one vector, matrices with enough row blocks for all SMs
+// ---------------------------------------------------------------------------
+// Same arithmetic as gemv_packed_kernel, different traversal.  A CTA owns whole row
+// blocks (so no block is shared between CTAs); inside it warp w owns the scale groups
+// w, w+16, w+32, ... and walks DOWN the CTA's row blocks for each of them.  The B
+// operand of a group (the activations' digits) is loaded into registers once per
+// group and reused for every row block, the group's 2^e factor likewise, and each
+// warp stages only its own groups' activations in a private piece of shared memory,
+// so there is no CTA-wide barrier before the main loop.  Weight tiles arrive through a
+// per-warp cp.async ring (RING tiles of 544 bytes).  Up to 8 row blocks are accumulated
+// in registers at a time; the 16 warps' partial sums of a row block are added in warp
+// order at the end.
+constexpr int kMaxFused = TLLM_MAX_FUSED;   // matrices sharing x in one launch (q/k/v, gate/up)
+
+struct CwArgs {
+    const uint8_t* packed[kMaxFused];
+    half* y[kMaxFused];             // half [rows[i]]
+    int rows[kMaxFused];
+    int rb_start[kMaxFused + 1];    // first row block of matrix i in the concatenated row-block space
+    int count;                      // matrices in this launch
+    const void* x;                  // half [cols] or int8 [cols], shared by all matrices
+    float in_scale;
+    int cols, groups;
+    int part_q, part_r;     // row blocks = gridDim.x * part_q + part_r
+    int gpw;                // groups per warp, ceil(groups / kWarps)
+    int off_xfac, off_part, off_ring;   // shared memory carve-up; digit staging starts at 0
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Four k32 steps of one tile with all operands in registers.
+template <bool I8>
+__device__ __forceinline__ void tile_mma_r(uint2 ca, uint2 cb, uint4 b01, uint4 b23, int mulA, int mulB, int& p0, int& p1)
+{
+    int d[4];
+    imma<I8, false>(d, prmt(kTabA_lo, kTabA_hi, ca.x), prmt(kTabA_lo, kTabA_hi, cb.x),
+                    prmt(kTabB_lo, kTabB_hi, ca.x), prmt(kTabB_lo, kTabB_hi, cb.x), b01.x, b01.y);
+    {
+        const uint32_t s0 = ca.x >> 16, s1 = cb.x >> 16;
+        imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, s0), prmt(kTabA_lo, kTabA_hi, s1),
+                       prmt(kTabB_lo, kTabB_hi, s0), prmt(kTabB_lo, kTabB_hi, s1), b01.z, b01.w);
+    }
+    imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, ca.y), prmt(kTabA_lo, kTabA_hi, cb.y),
+                   prmt(kTabB_lo, kTabB_hi, ca.y), prmt(kTabB_lo, kTabB_hi, cb.y), b23.x, b23.y);
+    {
+        const uint32_t s0 = ca.y >> 16, s1 = cb.y >> 16;
+        imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, s0), prmt(kTabA_lo, kTabA_hi, s1),
+                       prmt(kTabB_lo, kTabB_hi, s0), prmt(kTabB_lo, kTabB_hi, s1), b23.z, b23.w);
+    }
+    p0 = d[1] * mulA + d[0] * mulB;
+    p1 = d[3] * mulA + d[2] * mulB;
+}
+
+constexpr int kCwBlock = 8;      // row blocks accumulated in registers at a time
+
+template <int MODE, int RING>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_cw_kernel(const CwArgs a)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr bool I8 = (MODE == kI8);
+    static_assert(MODE != kF16B2, "one vector only");
+    static_assert((RING & (RING - 1)) == 0 && RING >= 2, "ring depth must be a power of two");
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    PHASE(0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.groups;
+    const int rb0 = part_start(blockIdx.x, a.part_q, a.part_r);
+    const int nrb = a.part_q + ((int)blockIdx.x < a.part_r ? 1 : 0);
+    const int ngw = (warp < G) ? ((G - warp + kWarps - 1) >> kWarpsLog2) : 0;   // groups of this warp
+    // matrix that owns row block R of the concatenated space
+    auto which = [&](int R) {
+        int i = 0;
+#pragma unroll
+        for (int j = 1; j < kMaxFused; j++)
+            if (j < a.count && R >= a.rb_start[j]) i = j;
+        return i;
+    };
+    const int nblk = (nrb + kCwBlock - 1) / kCwBlock;
+    const int ntiles = ngw * nrb;
+
+    uint32_t* stage = reinterpret_cast<uint32_t*>(smem) + warp * a.gpw * 128;   // 512 bytes per group
+    float* xfs = reinterpret_cast<float*>(smem + a.off_xfac) + warp * a.gpw;
+    float* part = reinterpret_cast<float*>(smem + a.off_part);                  // [row block][warp][32]
+    const uint32_t ring = smem_addr(smem + a.off_ring) + warp * (RING * kTileBytes);
+    const uint8_t* ring_p = smem + a.off_ring + warp * (RING * kTileBytes);
+
+    // ---- weight fetch, RING-1 tiles ahead of the arithmetic --------------------------
+    int fcnt = 0, fblk = 0, fgi = 0, fri = 0;
+    auto fetch = [&]() {
+        if (fcnt < ntiles) {
+            const int rb = rb0 + fblk * kCwBlock + fri, g = warp + (fgi << kWarpsLog2);
+            const int mi = which(rb);
+            const uint8_t* src = a.packed[mi] + ((size_t)(rb - a.rb_start[mi]) * G + g) * kTileBytes;
+            const uint32_t dst = ring + (fcnt & (RING - 1)) * kTileBytes;
+            cp_async16(dst + lane * 16, src + lane * 16);
+            if (lane < kTileBytes / 16 - 32) cp_async16(dst + 512 + lane * 16, src + 512 + lane * 16);
+            fcnt++;
+            if (++fri == min(kCwBlock, nrb - fblk * kCwBlock)) {
+                fri = 0;
+                if (++fgi == ngw) {
+                    fgi = 0;
+                    fblk++;
+                }
+            }
+        }
+        cp_async_commit();       // one group per tile slot, possibly empty
+    };
+#pragma unroll
+    for (int s = 0; s < RING - 1; s++) fetch();
+
+    // ---- everything below may depend on the previous kernel in the stream -------
+    PHASE(1);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    PHASE(2);
+
+    if (!I8) {
+        // this warp's groups only: digits in B-operand order, 512 bytes per group
+        const half* x = reinterpret_cast<const half*>(a.x);
+        for (int gi = 0; gi < ngw; gi++) {
+            const int g = warp + (gi << kWarpsLog2);
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (size_t)g * kGroup) + lane);
+            const float2 f0 = __half22float2(*reinterpret_cast<const half2*>(&raw.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const half2*>(&raw.y));
+            float m = fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y)));
+            m = warp_max(m);
+            const int e = max((int)((__float_as_uint(m) >> 23) & 0xffu) - 126, -24);
+            const float up = (m > 0.f) ? __uint_as_float((uint32_t)(22 - e + 127) << 23) : 0.f;
+            const float dn = (m > 0.f) ? __uint_as_float((uint32_t)(e - 22 + 127) << 23) : 0.f;
+            uint32_t w0, w1, w2;
+            quad_digits(f0.x, f0.y, f1.x, f1.y, up, w0, w1, w2);
+            // quad `lane` of the group: k32 step lane/8, k-slot 4*(lane%8)
+            const int m4 = lane >> 3, tq = lane & 7;
+            uint32_t* p = stage + ((gi * 2 + (m4 >> 1)) * 16 + (tq & 3)) * 4 + (m4 & 1) * 2 + (tq >> 2);
+            p[0 * 16] = w0;
+            p[1 * 16] = w1;
+            p[2 * 16] = w2;
+            p[3 * 16] = 0x01010101u;
+            if (lane == 0) xfs[gi] = dn;
+        }
+    }
+    __syncwarp();
+    PHASE(3);
+
+    const int t = lane & 3, gq = lane >> 2;
+    int mulA, mulB;
+    if (I8) {
+        mulA = 0;
+        mulB = (t == 0) ? 1 : 0;
+    } else {
+        mulA = (t >= 2) ? 0 : ((t & 1) ? -(1 << 23) : 256);
+        mulB = (t >= 2) ? 0 : ((t & 1) ? 65536 : 1);
+    }
+
+    int cnt = 0;
+    for (int blk = 0; blk < nblk; blk++) {
+        const int nr = min(kCwBlock, nrb - blk * kCwBlock);
+        float acc[kCwBlock][2];
+#pragma unroll
+        for (int r = 0; r < kCwBlock; r++) acc[r][0] = acc[r][1] = 0.f;
+
+        for (int gi = 0; gi < ngw; gi++) {
+            uint4 b01, b23;
+            float f;
+            if (I8) {
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(a.x) + (warp + (gi << kWarpsLog2)) * 32 + t;
+                b01 = make_uint4(__ldg(xw), __ldg(xw + 4), __ldg(xw + 8), __ldg(xw + 12));
+                b23 = make_uint4(__ldg(xw + 16), __ldg(xw + 20), __ldg(xw + 24), __ldg(xw + 28));
+                f = 1.0f;
+            } else {
+                const uint4* s4 = reinterpret_cast<const uint4*>(stage) + gi * 32 + (lane & 15);
+                b01 = s4[0];
+                b23 = s4[16];
+                f = xfs[gi];
+            }
+#pragma unroll
+            for (int r = 0; r < kCwBlock; r++) {
+                if (r < nr) {
+                    cp_async_wait<RING - 2>();       // tile `cnt` has landed
+                    __syncwarp();                    // ... for all lanes, and tile cnt-1 is no longer read
+                    fetch();                         // refill the slot of tile cnt-1
+                    const uint8_t* tp = ring_p + (cnt & (RING - 1)) * kTileBytes;
+                    const uint2 ca = *reinterpret_cast<const uint2*>(tp + lane * 8);
+                    const uint2 cb = *reinterpret_cast<const uint2*>(tp + 256 + lane * 8);
+                    const float2 sc = __half22float2(*reinterpret_cast<const half2*>(tp + kTileCodeBytes + gq * 4));
+                    int p0, p1;
+                    tile_mma_r<I8>(ca, cb, b01, b23, mulA, mulB, p0, p1);
+                    acc[r][0] = fmaf((float)p0, sc.x * f, acc[r][0]);
+                    acc[r][1] = fmaf((float)p1, sc.y * f, acc[r][1]);
+                    cnt++;
+                }
+            }
+        }
+        // this warp's sums for the block's row blocks (lanes t and t^1 hold the two digit halves)
+#pragma unroll
+        for (int r = 0; r < kCwBlock; r++) {
+            if (r < nr) {
+                const float v0 = acc[r][0] + __shfl_xor_sync(0xffffffffu, acc[r][0], 1);
+                const float v1 = acc[r][1] + __shfl_xor_sync(0xffffffffu, acc[r][1], 1);
+                if (t == 0 && ngw > 0) {
+                    float* pu = part + ((blk * kCwBlock + r) * kWarps + warp) * 32;
+                    pu[gq * 2] = v0;
+                    pu[(gq + 8) * 2] = v1;
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    PHASE(4);
+    __syncthreads();
+    PHASE(5);
+
+    // ---- add the warps' partial sums in warp order and store -------------------------
+    const float oscale = I8 ? a.in_scale : 1.0f;
+    const int nwarps_used = min(kWarps, G);
+    for (int rbl = warp; rbl < nrb; rbl += kWarps) {
+        if ((lane & 1) == 0) {
+            float s = 0.f;
+            for (int w = 0; w < nwarps_used; w++) s += part[(rbl * kWarps + w) * 32 + lane];
+            const int mi = which(rb0 + rbl);
+            const int r = (rb0 + rbl - a.rb_start[mi]) * 16 + (lane >> 1);
+            if (r < a.rows[mi]) a.y[mi][r] = __float2half_rn(s * oscale);
+        }
+    }
+    PHASE(6);
+}
+
+// ---------------------------------------------------------------------------
 // Repack: reference layout -> packed layout, and back
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int tern_at(const uint32_t* nz, const uint32_t* sg, int rows, int wpr, int r, int k)
@@ -729,9 +964,115 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     }
 }
 
+// Column-walk kernel: usable when whole row blocks balance the SMs and every warp has a group.
+static bool cw_eligible_rb(int sms, int nrb, int cols)
+{
+    const int groups = cols / kGroup;
+    int grid = sms < kMaxCtas ? sms : kMaxCtas;
+    if (nrb < grid || groups < kWarps) return false;
+    const int per = (nrb + grid - 1) / grid;
+    return (double)nrb / ((double)per * grid) >= 0.8;
+}
+static bool cw_eligible(int sms, int rows, int cols) { return cw_eligible_rb(sms, (rows + 15) / 16, cols); }
+
+template <int MODE, int RING>
+static int launch_cw_t(const CwArgs& a, int grid, size_t smem, cudaStream_t stream)
+{
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr[dev]) {
+        cudaFuncSetAttribute(gemv_cw_kernel<MODE, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cw_kernel<MODE, RING>, a);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLLM_ERR_LAUNCH, "gemv_cw launch: %s", cudaGetErrorString(e));
+    }
+    return TLLM_OK;
+}
+
+static int launch_cw_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, const void* x,
+                           float in_scale, int mode, int cols, int sms, cudaStream_t stream)
+{
+    CwArgs a = {};
+    int nrb = 0;
+    for (int i = 0; i < count; i++) {
+        a.packed[i] = packed[i];
+        a.y[i] = y[i];
+        a.rows[i] = rows[i];
+        a.rb_start[i] = nrb;
+        nrb += (rows[i] + 15) / 16;
+    }
+    for (int i = count; i <= kMaxFused; i++) a.rb_start[i] = nrb;
+    a.count = count;
+    a.x = x;
+    a.in_scale = in_scale;
+    a.cols = cols;
+    a.groups = cols / kGroup;
+    const int grid = sms < kMaxCtas ? sms : kMaxCtas;
+    a.part_q = nrb / grid;
+    a.part_r = nrb % grid;
+    a.gpw = (a.groups + kWarps - 1) / kWarps;
+    // shared memory: digit staging (512 B per group) | group factors | partial sums | rings
+    size_t off = (mode == kI8) ? 0 : (size_t)kWarps * a.gpw * 512;
+    a.off_xfac = (int)off;
+    off += (size_t)kWarps * a.gpw * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_part = (int)off;
+    off += (size_t)(a.part_q + 1) * kWarps * 32 * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_ring = (int)off;
+    // deeper ring while two CTAs still fit in one SM's shared memory
+    const size_t budget = (size_t)110 * 1024;
+    const bool deep = off + (size_t)kWarps * 8 * kTileBytes <= budget;
+    off += (size_t)kWarps * (deep ? 8 : 4) * kTileBytes;
+    if (off > 227 * 1024) return TLLM_ERR_SIZE;           // caller falls back to the general streaming kernel
+    if (mode == kI8) return deep ? launch_cw_t<kI8, 8>(a, grid, off, stream) : launch_cw_t<kI8, 4>(a, grid, off, stream);
+    return deep ? launch_cw_t<kF16B1, 8>(a, grid, off, stream) : launch_cw_t<kF16B1, 4>(a, grid, off, stream);
+}
+
+// Several matrices that share x and the column count (q/k/v; gate/up) in one launch when
+// together they fill the SMs; otherwise one launch each.
+int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
+                             const half* x, cudaStream_t stream)
+{
+    DeviceScratch* s = nullptr;
+    int st = get_scratch(&s);
+    if (st) return st;
+    // One fused launch pays off when some matrix alone cannot fill the SMs with whole row
+    // blocks (k and v of grouped-query attention); matrices that can are streamed one by
+    // one by the general kernel, which is the faster of the two for them.
+    int nrb = 0;
+    bool small = false;
+    for (int i = 0; i < count; i++) {
+        nrb += (rows[i] + 15) / 16;
+        small = small || !cw_eligible(s->sms, rows[i], cols);
+    }
+    if (small && count >= 2 && count <= kMaxFused && cw_eligible_rb(s->sms, nrb, cols)) {
+        st = launch_cw_multi(count, packed, y, rows, x, 1.0f, kF16B1, cols, s->sms, stream);
+        if (st != TLLM_ERR_SIZE) return st;
+    }
+    for (int i = 0; i < count; i++)
+        if ((st = launch_gemv_packed(packed[i], x, y[i], 1, rows[i], cols, stream))) return st;
+    return TLLM_OK;
+}
+
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
                        cudaStream_t stream)
 {
+
     // two vectors share one pass over the weights; larger batches take ceil(B/2) passes
     for (int b0 = 0; b0 < batch; b0 += 2) {
         const int nb = (batch - b0 >= 2) ? 2 : 1;
@@ -842,6 +1183,7 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
 int launch_gemv_int8_packed(const uint8_t* packed, const int8_t* xq, float in_scale, half* y, int rows,
                             int cols, cudaStream_t stream)
 {
+
     return launch_packed_once(packed, xq, y, in_scale, kI8, 1, rows, cols, stream);
 }
 

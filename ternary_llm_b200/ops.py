@@ -155,6 +155,21 @@ def ternary_gemv_int8_packed(w: PreparedWeight, input_int8, input_scale: float, 
                                                      w.rows, w.cols, _stream()))
 
 
+def ternary_gemv_packed_multi(weights, input, outputs) -> None:
+    """y_i = W_i x for up to 4 prepared matrices sharing the vector x (q/k/v, gate/up)
+    in one launch."""
+    import ctypes
+    n = len(weights)
+    cols = weights[0].cols
+    if any(w.cols != cols for w in weights) or len(outputs) != n:
+        raise ValueError("fused matrices must share the column count and have one output each")
+    packed = (ctypes.c_void_p * n)(*[w.packed.data_ptr() for w in weights])
+    ys = (ctypes.c_void_p * n)(*[_chk(y, torch.float16, "output") for y in outputs])
+    rows = (ctypes.c_int * n)(*[w.rows for w in weights])
+    _lib.check(_lib.lib().tllm_b200_gemv_packed_multi(n, packed, ys, rows, cols,
+                                                      _chk(input, torch.float16, "input"), _stream()))
+
+
 def ternary_gemm_packed(A, w: PreparedWeight, C, M: int) -> None:
     """C[M,N] = A[M,K] . W^T on prepared weights (tcgen05 kernel for M > 16)."""
     _lib.check(_lib.lib().tllm_b200_gemm_packed(_chk(A, torch.float16, "A"), w.packed.data_ptr(),

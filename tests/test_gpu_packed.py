@@ -187,3 +187,29 @@ def test_gemv_packed_linearity_at_full_size():
     yn = _run_packed(w, -x)
     d = np.abs(yn.astype(np.float32) + y1.astype(np.float32))
     assert (d <= np.abs(y1.astype(np.float32)) * 2.0 ** -10 + 1e-7).all() and (d > 0).mean() < 0.01
+
+
+@pytest.mark.parametrize("shapes,k", [([4096, 1024, 1024], 4096), ([14336, 14336], 4096), ([64, 48], 512),
+                                      ([2048, 512, 512, 100], 2048)])
+def test_gemv_packed_multi_equals_separate_calls(shapes, k):
+    """q/k/v- and gate/up-style fused launches give exactly what separate calls give."""
+    rng = np.random.default_rng(sum(shapes) + k)
+    x = rng.standard_normal(k).astype(np.float16)
+    dx = _dev(x)
+    ws, mats = [], []
+    for i, n in enumerate(shapes):
+        nz, sg, sc = tl.pack.random_ternary_weight(n, k, seed=100 + i)
+        mats.append((nz, sg, sc))
+        ws.append(_prep(nz, sg, sc))
+    fused = [torch.full((n,), float("nan"), dtype=torch.float16, device=DEV) for n in shapes]
+    tl.ternary_gemv_packed_multi(ws, dx, fused)
+    single = [torch.zeros(n, dtype=torch.float16, device=DEV) for n in shapes]
+    for w, y in zip(ws, single):
+        tl.ternary_gemv_packed(w, dx, y, 1)
+    torch.cuda.synchronize()
+    for (nz, sg, sc), yf, ys in zip(mats, fused, single):
+        # the fused launch may add the K groups in a different order: at most a last-place difference
+        d = (yf.float() - ys.float()).abs()
+        assert bool((d <= ys.float().abs() * 2.0 ** -10 + 1e-6).all())
+        y64, bound = exact_and_bound(nz, sg, sc, x)
+        assert_within(yf.cpu().numpy(), y64, bound, "fused", slack=_half_ulp(y64))

@@ -4,9 +4,11 @@ tllm_b200_gemv_packed_noalloc exists for hosts that cannot allow a library to ca
 cudaMalloc (their own arena owns the device memory, or allocation is forbidden where
 the call is made); its split-K scratch is a fixed array inside the library.  This
 test calls it straight through the C ABI, twice in a row on each shape, and compares
-with tllm_b200_gemv_packed on the same prepared weights.  Both run the same kernel,
-so the results must agree bit for bit, well inside the 2e-3 * sum|scale*x| tolerance
-the other tests use; the second call checks that the shared scratch is left reusable.
+with tllm_b200_gemv_packed on the same prepared weights.  The two may add the K
+groups in a different order, so they are compared to within one FP16 last place and
+each against the oracle with the 2e-3 * sum|scale*x| tolerance the other tests use;
+the two calls in a row must agree exactly with each other, which checks that the
+shared scratch is left reusable.
 The file name sorts last so that a stop-at-first-failure run has already executed
 every other test.
 """
@@ -51,9 +53,11 @@ def test_noalloc_matches_regular_entry_point_twice(n, k):
         _lib.check(h.tllm_b200_gemv_packed_noalloc(w.packed.data_ptr(), dx.data_ptr(), y.data_ptr(), n, k, stream))
         outs.append(y)
     torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
     for y in outs:
         assert not torch.isnan(y).any()
-        assert torch.equal(y, y_ref)
+        d = (y.float() - y_ref.float()).abs()
+        assert bool((d <= y_ref.float().abs() * 2.0 ** -10 + 1e-6).all())
     y64, bound = exact_and_bound(nz, sg, sc, x[0])
     half_ulp = 0.5 * 2.0 ** (np.floor(np.log2(np.maximum(np.abs(y64), 2.0 ** -14))) - 10)
     assert_within(outs[1].cpu().numpy(), y64, bound, f"noalloc {n}x{k}", slack=half_ulp)
