@@ -213,3 +213,24 @@ def test_gemv_packed_multi_equals_separate_calls(shapes, k):
         assert bool((d <= ys.float().abs() * 2.0 ** -10 + 1e-6).all())
         y64, bound = exact_and_bound(nz, sg, sc, x)
         assert_within(yf.cpu().numpy(), y64, bound, "fused", slack=_half_ulp(y64))
+
+
+def test_tllm_file_to_prepared_weights(tmp_path):
+    """Writer -> file -> loader -> kernels: every projection of a small random-init model."""
+    from ternary_llm_b200 import tllm_format as tf
+    cfg = tf.TllmConfig(vocab_size=64, hidden_dim=256, intermediate_dim=512, n_layers=2, n_heads=4,
+                        n_kv_heads=2, head_dim=64, max_seq_len=64)
+    m = tf.random_model(cfg, seed=11)
+    path = str(tmp_path / "tiny.tllm")
+    tf.write_tllm(path, m)
+    cfg2, layers = tf.load_projections(path, DEV)
+    assert cfg2 == cfg and len(layers) == 2
+    rng = np.random.default_rng(5)
+    for li, layer in enumerate(layers):
+        for name in tf.PROJ_NAMES:
+            w = layer[name]
+            t = m.layers[li][name]
+            x = rng.standard_normal((1, w.cols)).astype(np.float16)
+            y = _run_packed(w, x)
+            y64, bound = exact_and_bound(t.nonzero_masks, t.sign_masks, t.scales, x)
+            assert_within(y, y64, bound, f"L{li}.{name}", slack=_half_ulp(y64))
