@@ -572,6 +572,47 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """A small single-kernel case for profilers: `gemv:NxK[:copies]`, `gemv_int8:NxK[:copies]`
+    or `gemm:MxNxK`.  Distinct matrices are cycled so that the weights come from HBM."""
+    import torch
+
+    import ternary_llm_b200 as tl
+    from ternary_llm_b200 import synth
+    kind, dims, *rest = args.case.split(":")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if kind in ("gemv", "gemv_int8"):
+        n, k = (int(v) for v in dims.split("x"))
+        copies = int(rest[0]) if rest else 12
+        ws = []
+        for i in range(copies):
+            nz, sg, sc = synth.random_ternary_weight(n, k, seed=i, device=dev)
+            ws.append(tl.PreparedWeight(nz, sg, sc, n, k, register=False, keep_source=False))
+        x = torch.randn(k, device=dev).half()
+        xq = torch.randint(-127, 128, (k,), device=dev, dtype=torch.int8)
+        y = torch.zeros(n, device=dev, dtype=torch.float16)
+        for _ in range(2):
+            for w in ws:
+                if kind == "gemv":
+                    tl.ternary_gemv_packed(w, x, y, 1)
+                else:
+                    tl.ternary_gemv_int8_packed(w, xq, 0.01, y)
+    elif kind == "gemm":
+        m, n, k = (int(v) for v in dims.split("x"))
+        nz, sg, sc = synth.random_ternary_weight(n, k, seed=0, device=dev)
+        w = tl.PreparedWeight(nz, sg, sc, n, k, register=False, keep_source=False)
+        a = torch.randn(m, k, device=dev).half()
+        c = torch.zeros(m, n, device=dev, dtype=torch.float16)
+        for _ in range(4):
+            tl.ternary_gemm_packed(a, w, c, m)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    print(json.dumps({"case": args.case, "status": "ok"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -581,7 +622,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="N>1 only: layer count override for quick checks (0 = the full 80)")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
+                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemm:MxNxK")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.impl == "reference":
         run_reference(args)
     else:
