@@ -232,13 +232,10 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
         n = 0
         for mats in layers:
             q, k, v, o, g, u, d = mats
-            tl.ternary_gemv_packed(q, x_h, yq)
-            tl.ternary_gemv_packed(k, x_h, yk)
-            tl.ternary_gemv_packed(v, x_h, yv)
+            tl.ternary_gemv_packed_multi([q, k, v], x_h, [yq, yk, yv])   # column shards, one input
             tl.ternary_gemv_packed(o, x_attn, yo)        # row-parallel: partial sums ...
             dist.all_reduce(yo)                          # ... combined over NVLink
-            tl.ternary_gemv_packed(g, x_h, yg)
-            tl.ternary_gemv_packed(u, x_h, yu)
+            tl.ternary_gemv_packed_multi([g, u], x_h, [yg, yu])
             tl.ternary_gemv_packed(d, x_ffn, yd)
             dist.all_reduce(yd)
             n += 7
@@ -551,7 +548,8 @@ def run_ours(args):
                        "launch": "CUDA graph replay of the whole step; q/k/v fused into one launch per layer (they share the input vector), gate/up issued through the same fused entry point",
                        "parallelism": "independent replicas per GPU" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": 15628288, "peak_kind": peak_kind,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in profiles/gemv_packed_14336x4096_b1.md",
                          "kernel": "gemv 14336x4096 batch 1", "bytes_per_launch": rb,
                          "us_per_launch": ms_roof * 1e3,
                          "frac_of_nominal_8000": achieved / 8000.0},
