@@ -228,16 +228,24 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
     yu = torch.zeros(I70 // world, dtype=torch.float16, device=dev)
     yd = torch.zeros(H70, dtype=torch.float16, device=dev)
 
+    fused = args.allreduce == "fused"
+    ar = tl.FusedAllReduce(dist.group.WORLD, H70, dev) if fused else None
+
+    def row_parallel(w, x_local, y):
+        if fused:      # partial sums exchanged by the GEMV kernel itself over peer memory
+            tl.ternary_gemv_packed_allreduce(w, x_local, y, ar)
+        else:          # library route: GEMV, then NCCL all-reduce of the FP16 vector
+            tl.ternary_gemv_packed(w, x_local, y)
+            dist.all_reduce(y)
+
     def launch_step():
         n = 0
         for mats in layers:
             q, k, v, o, g, u, d = mats
             tl.ternary_gemv_packed_multi([q, k, v], x_h, [yq, yk, yv])   # column shards, one input
-            tl.ternary_gemv_packed(o, x_attn, yo)        # row-parallel: partial sums ...
-            dist.all_reduce(yo)                          # ... combined over NVLink
+            row_parallel(o, x_attn, yo)
             tl.ternary_gemv_packed_multi([g, u], x_h, [yg, yu])
-            tl.ternary_gemv_packed(d, x_ffn, yd)
-            dist.all_reduce(yd)
+            row_parallel(d, x_ffn, yd)
             n += 7
         return n
 
@@ -258,7 +266,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
                 launch_step()
-            graph, mode = g, "CUDA graph replay of the whole step (NCCL all-reduce captured)"
+            graph, mode = g, "CUDA graph replay of the whole step"
         except Exception as e:      # capture of the collective is not available: launch eagerly
             mode = f"eager launches (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
@@ -331,7 +339,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 MMA (exact s32 group sums), f32 accumulate", "data": "synthetic",
             "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, %d layers), batch 1, decode-style pass" % n_layers,
-                       "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, NCCL all-reduce of the 8192-vector after o and after down (160 per step)",
+                       "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, all-reduce of the 8192-vector after o and after down (160 per step): " + ("fused into the row-parallel GEMV kernel (peer stores over NVLink, flags, local sum)" if fused else "NCCL"),
                        "gemv_per_step_per_gpu": launches, "bytes_per_step": step_bytes,
                        "l2": f"{per_gpu_bytes/1e9:.2f} GB of distinct weights per GPU per step (> 126 MB L2), no flush needed",
                        "launch": mode},
@@ -619,6 +627,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="N>1 only: layer count override for quick checks (0 = the full 80)")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
                     "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemm:MxNxK")

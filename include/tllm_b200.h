@@ -42,7 +42,9 @@ extern "C" {
 
 #define TLLM_GROUP_SIZE       128
 #define TLLM_MAX_BATCH        16
-#define TLLM_MAX_FUSED        4    /* matrices per tllm_b200_gemv_packed_multi call */
+#define TLLM_MAX_FUSED        4
+#define TLLM_MAX_PEERS        8    /* ranks of a fused all-reduce (one 8-GPU NVSwitch box) */
+#define TLLM_AR_MAX_CTAS      256  /* length of the per-rank launch-counter array */    /* matrices per tllm_b200_gemv_packed_multi call */
 
 /* Text for a status code; never NULL. */
 const char* tllm_b200_status_string(int status);
@@ -168,6 +170,27 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
  */
 int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows,
                                 int cols, const void* x, void* stream);
+
+/*
+ * Row-parallel GEMV of a tensor-parallel layer (o_proj, down_proj: each rank holds a
+ * 128-aligned K range of the matrix and the matching slice of x) with the all-reduce
+ * FUSED into the kernel: every rank runs this call on its shard; each CTA stores its
+ * FP32 partial sums into all ranks' receive buffers over NVLink as 8-byte {value, launch
+ * number} words (plain peer stores; the launch number is the arrival flag, so there is no
+ * fence and no separate flag round), polls -- bounded -- its OWN memory for the other
+ * ranks' words of the same rows, adds the contributions in rank order and writes the FP16
+ * result y[rows], identical on all ranks.  No counterpart in the reference (which is
+ * single-GPU); it replaces GEMV + ncclAllReduce.
+ *   peer_recv[d] : rank d's receive buffer, 8-byte words [2][world][rows_max], as mapped in
+ *                  THIS process (peer / symmetric memory), zeroed before first use
+ *   epoch_local  : this rank's launch counters, uint32 [TLLM_AR_MAX_CTAS], zeroed
+ * All ranks must issue the same sequence of these calls.  rows >= 16 x (number of SMs);
+ * otherwise TLLM_ERR_SHAPE (use tllm_b200_gemv_packed + a library all-reduce).  A wait
+ * that expires sets the device error flag (tllm_b200_check_device_errors).
+ */
+int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, int rows, int cols,
+                                    int rank, int world, void* const* peer_recv, void* epoch_local,
+                                    int rows_max, void* stream);
 
 /*
  * tllm_b200_gemv_packed for one FP16 vector, for callers that cannot let a library

@@ -246,6 +246,20 @@ int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* cons
                                     (const half*)x, (cudaStream_t)stream);
 }
 
+int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, int rows, int cols, int rank, int world,
+                                    void* const* peer_recv, void* epoch_local, int rows_max, void* stream)
+{
+    int st = check_packed_call(packed, x, y, rows, cols);
+    if (st) return st;
+    if (!peer_recv || !epoch_local) return fail(TLLM_ERR_NULL, "null peer buffer table");
+    for (int d = 0; d < world && d < TLLM_MAX_PEERS; d++) {
+        if (!peer_recv[d]) return fail(TLLM_ERR_NULL, "null receive buffer of rank %d", d);
+        if (misaligned(peer_recv[d], 8)) return fail(TLLM_ERR_ALIGN, "receive buffers must be 8-byte aligned");
+    }
+    return launch_gemv_packed_allreduce((const uint8_t*)packed, (const half*)x, (half*)y, rows, cols, rank, world,
+                                        peer_recv, epoch_local, rows_max, (cudaStream_t)stream);
+}
+
 int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y, int rows, int cols, void* stream)
 {
     int st = check_packed_call(packed, x, y, rows, cols);

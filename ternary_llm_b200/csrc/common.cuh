@@ -41,6 +41,9 @@ int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint3
 int weight_register(const void* nz, const uint8_t* packed, int rows, int cols);
 int weight_unregister(const void* nz);
 int device_error_check(cudaStream_t stream);
+int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, int rows, int cols, int rank,
+                                 int world, void* const* peer_recv, void* epoch_local, int rows_max,
+                                 cudaStream_t stream);
 int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
                              const half* x, cudaStream_t stream);
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,

@@ -53,6 +53,7 @@ constexpr int kSlotBytes = kSlotTiles * kTileBytes;   // 2176
 constexpr int kRing = 2;                              // slots per warp
 constexpr int kTickets = 64;                          // independent scratch regions
 constexpr int kMaxCtas = 256;
+constexpr int kMaxPeers = TLLM_MAX_PEERS;
 
 enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2 };
 
@@ -70,6 +71,11 @@ struct GemvArgs {
     int* err;               // device error flag (0 = none)
     // shared memory carve-up (byte offsets)
     int off_xfac, off_part, off_ring, off_bar;
+    // Fused all-reduce over peer memory (row-parallel shards of a tensor-parallel layer);
+    // ar_world == 0 switches it off.  Every rank runs the same launch on its own shard.
+    int ar_world, ar_rank, ar_rows_max;
+    uint2* ar_recv[kMaxPeers];        // rank d's receive buffer  {value, launch number} [2][world][ar_rows_max]
+    unsigned* ar_epoch;               // this rank's launch counters, uint [kMaxCtas]
 };
 
 #ifdef TLLM_PROFILE_PHASES
@@ -451,6 +457,59 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     const int nb = (MODE == kF16B2) ? a.batch : 1;
     const float oscale = I8 ? a.in_scale : 1.0f;
     float* myrec = a.ws + (size_t)blockIdx.x * 64;
+
+    if (a.ar_world > 0) {
+        // ---- fused all-reduce: my partial sums go straight into every rank's receive
+        // buffer over NVLink as 8-byte {value, launch number} words -- the store of a word
+        // is atomic, so the launch number doubles as the arrival flag and no fence or
+        // separate flag round is needed.  Each CTA then polls (bounded) its OWN memory for
+        // the other ranks' words of the same rows -- every rank runs this launch with the
+        // same partition -- and adds the contributions in rank order.  Buffers alternate
+        // with the launch parity, so a rank that runs one launch ahead never overwrites
+        // words that are still being read.
+        const unsigned epoch = a.ar_epoch[blockIdx.x] + 1u;
+        const unsigned par = epoch & 1u;
+        const size_t slot = (size_t)(par * a.ar_world + a.ar_rank) * a.ar_rows_max;
+        for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
+            const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);
+            const int wa = warp_of(ta - t0, n), wb = warp_of(tb - 1 - t0, n);
+            float s = 0.f;
+            for (int w = wa; w <= wb; w++)
+                if (warp_start(w + 1, n) > warp_start(w, n)) s += part[((r_b - rb_first) + w) * 32 + lane];
+            const int r = r_b * 16 + (lane >> 1);
+            if ((lane & 1) == 0 && r < a.rows) {
+                const uint2 word = make_uint2(__float_as_uint(s), epoch);
+                for (int d = 0; d < a.ar_world; d++) {
+                    uint2* dst = a.ar_recv[d] + slot + r;
+                    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(word.x), "r"(word.y) : "memory");
+                }
+            }
+        }
+        const int r_lo = rb_first * 16, r_hi = min(a.rows, (rb_last + 1) * 16);
+        const uint2* recv = a.ar_recv[a.ar_rank] + (size_t)par * a.ar_world * a.ar_rows_max;
+        bool ok_ar = true;
+        for (int r = r_lo + tid; r < r_hi; r += kThreads) {
+            float v = 0.f;
+            for (int d = 0; d < a.ar_world; d++) {
+                const uint2* src = recv + (size_t)d * a.ar_rows_max + r;
+                uint32_t val = 0, tag = 0;
+#pragma unroll 1
+                for (int i = 0; i < (1 << 21); i++) {       // about half a second at most
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(tag) : "l"(src) : "memory");
+                    if (tag == epoch) break;
+                    __nanosleep(32);
+                }
+                ok_ar = ok_ar && (tag == epoch);
+                v += __uint_as_float(val);
+            }
+            a.y[r] = __float2half_rn(v);
+        }
+        if (!ok_ar) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+        __syncthreads();
+        if (tid == 0) a.ar_epoch[blockIdx.x] = epoch;
+        PHASE(6);
+        return;
+    }
 
     for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
         const int row = lane >> 1, b = lane & 1;
@@ -1178,6 +1237,57 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
         return fail(TLLM_ERR_LAUNCH, "clearing the scratch counters failed");
     }
     return launch_mode<kF16B1>(a, grid, off, stream, nullptr);
+}
+
+// Row-parallel GEMV with the all-reduce over peer memory fused into its epilogue.
+int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, int rows, int cols, int rank,
+                                 int world, void* const* peer_recv, void* epoch_local, int rows_max,
+                                 cudaStream_t stream)
+{
+    DeviceScratch* s = nullptr;
+    int st = get_scratch(&s);
+    if (st) return st;
+    if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world)
+        return fail(TLLM_ERR_SHAPE, "rank %d / world %d outside 2..%d ranks", rank, world, kMaxPeers);
+    if (rows > rows_max) return fail(TLLM_ERR_SIZE, "rows=%d exceeds the receive buffers (%d rows)", rows, rows_max);
+    GemvArgs a = {};
+    a.packed = packed;
+    a.x = x;
+    a.y = y;
+    a.in_scale = 1.0f;
+    a.rows = rows;
+    a.cols = cols;
+    a.groups = cols / kGroup;
+    a.batch = 1;
+    const int nrb = (rows + 15) / 16;
+    const int grid = s->sms < kMaxCtas ? s->sms : kMaxCtas;
+    const int per_cta_rb = (nrb + grid - 1) / grid;
+    if (nrb < grid || (double)nrb / ((double)per_cta_rb * grid) < 0.8)
+        return fail(TLLM_ERR_SHAPE, "rows=%d: the fused all-reduce needs at least one 16-row block per SM", rows);
+    a.aligned = 1;
+    a.part_q = nrb / grid;
+    a.part_r = nrb % grid;
+    a.ws = s->ws;                       // unused in the aligned split
+    a.counters = s->counters;
+    a.err = s->misc + 1;
+    a.ar_world = world;
+    a.ar_rank = rank;
+    a.ar_rows_max = rows_max;
+    for (int d = 0; d < world; d++) a.ar_recv[d] = static_cast<uint2*>(peer_recv[d]);
+    a.ar_epoch = static_cast<unsigned*>(epoch_local);
+    size_t off = ((size_t)a.groups * 2 * 16 * 16 + 15) & ~(size_t)15;
+    a.off_xfac = (int)off;
+    off += (size_t)2 * a.groups * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_part = (int)off;
+    off += (size_t)(a.part_q + 1 + kWarps) * 32 * sizeof(float);
+    off = (off + 15) & ~(size_t)15;
+    a.off_ring = (int)off;
+    off += (size_t)kWarps * kRing * kSlotBytes;
+    a.off_bar = (int)off;
+    off += (size_t)kWarps * kRing * 8;
+    if (off > 227 * 1024) return fail(TLLM_ERR_SHAPE, "cols=%d needs %zu bytes of shared memory", cols, off);
+    return launch_mode<kF16B1>(a, grid, off, stream, s);
 }
 
 int launch_gemv_int8_packed(const uint8_t* packed, const int8_t* xq, float in_scale, half* y, int rows,

@@ -170,6 +170,43 @@ def ternary_gemv_packed_multi(weights, input, outputs) -> None:
                                                       _chk(input, torch.float16, "input"), _stream()))
 
 
+AR_MAX_CTAS = 256
+
+
+class FusedAllReduce:
+    """Peer-memory buffers for tllm_b200_gemv_packed_allreduce, one per process group.
+
+    Allocates one symmetric-memory tensor per rank (the receive slots),
+    exchanges the mappings with torch's symmetric-memory rendezvous, and keeps the
+    per-rank pointer tables.  PyTorch is used for the mapping only; the data path is the
+    GEMV kernel's own peer stores."""
+
+    def __init__(self, group, rows_max: int, device):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rows_max = rows_max
+        recv_bytes = 2 * self.world * rows_max * 8          # {value, launch number} words, two parities
+        self.buf = symm_mem.empty(recv_bytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name if hasattr(group, "group_name") else group)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.recv = (ctypes.c_void_p * self.world)(*ptrs)
+        self.epoch = torch.zeros(AR_MAX_CTAS, dtype=torch.int32, device=device)
+
+
+def ternary_gemv_packed_allreduce(w: PreparedWeight, input, output, ar: FusedAllReduce) -> None:
+    """Row-parallel y = sum over ranks of W_r x_r with the all-reduce fused into the kernel."""
+    _lib.check(_lib.lib().tllm_b200_gemv_packed_allreduce(
+        w.packed.data_ptr(), _chk(input, torch.float16, "input"), _chk(output, torch.float16, "output"),
+        w.rows, w.cols, ar.rank, ar.world, ar.recv, ar.epoch.data_ptr(), ar.rows_max, _stream()))
+
+
 def ternary_gemm_packed(A, w: PreparedWeight, C, M: int) -> None:
     """C[M,N] = A[M,K] . W^T on prepared weights (tcgen05 kernel for M > 16)."""
     _lib.check(_lib.lib().tllm_b200_gemm_packed(_chk(A, torch.float16, "A"), w.packed.data_ptr(),
