@@ -1,0 +1,73 @@
+#!/usr/bin/env python3
+"""End-to-end decode of a random-init ternary model through the REFERENCE engine's own
+Model/Transformer code (oracle/engine_main.cpp), once with the reference's ternary kernels
+and once with libtllm_b200.so in their place.  Not a pytest module; run on a GPU machine:
+
+    python tests/run_engine_e2e.py [--arch 1b|tiny] [--prompt 512] [--decode 128]
+
+`1b` is the LLaMA-3.2-1B architecture of the benchmark definition (16 layers, hidden 2048,
+32/8 heads of 64, intermediate 8192, vocab 128256, FP16 embedding and lm_head); the weights
+are seeded random (W = 0.02*randn, ternarised per 128).  Prints both engines' timing lines
+and the agreement of their final logits."""
+import argparse
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from ternary_llm_b200 import tllm_format as tf  # noqa: E402
+
+ARCHS = {
+    "1b": dict(vocab_size=128256, hidden_dim=2048, intermediate_dim=8192, n_layers=16, n_heads=32, n_kv_heads=8,
+               head_dim=64, max_seq_len=1024, rope_theta=500000.0, rms_norm_eps=1e-5),
+    "tiny": dict(vocab_size=4096, hidden_dim=512, intermediate_dim=1024, n_layers=2, n_heads=8, n_kv_heads=2,
+                 head_dim=64, max_seq_len=256, rope_theta=500000.0, rms_norm_eps=1e-5),
+}
+
+
+def run_engines(model_path, n_prompt, n_decode, workdir):
+    out = {}
+    for name in ("engine_ref", "engine_tllm"):
+        exe = os.path.join(ROOT, "oracle", "_ref", name)
+        logits = os.path.join(workdir, name + ".logits")
+        r = subprocess.run([exe, model_path, str(n_prompt), str(n_decode), logits], capture_output=True, text=True,
+                           timeout=1200)
+        line = [l for l in r.stdout.splitlines() if l.startswith("prefill_ms")]
+        if r.returncode != 0 or not line:
+            raise RuntimeError(f"{name} failed: {r.stdout[-500:]} {r.stderr[-1500:]}")
+        fields = dict(kv.split("=", 1) for kv in line[0].split() if "=" in kv)
+        out[name] = (fields, np.fromfile(logits, dtype=np.float16).astype(np.float32))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="1b", choices=sorted(ARCHS))
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128)
+    args = ap.parse_args()
+    cfg = tf.TllmConfig(**ARCHS[args.arch])
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "model.tllm")
+        t0 = time.time()
+        tf.write_tllm(path, tf.random_model(cfg, seed=2026))
+        print(f"wrote {path}: {os.path.getsize(path) / 1e6:.1f} MB in {time.time() - t0:.1f} s", flush=True)
+        res = run_engines(path, args.prompt, args.decode, d)
+    for name, (fields, _) in res.items():
+        print(name, fields)
+    a, b = res["engine_ref"][1], res["engine_tllm"][1]
+    print(f"final logits: max |ref - tllm| = {np.abs(a - b).max():.4g}, max |ref| = {np.abs(a).max():.4g}, "
+          f"same last token: {res['engine_ref'][0]['last_token'] == res['engine_tllm'][0]['last_token']}")
+    r, t = float(res["engine_ref"][0]["tok_per_s"]), float(res["engine_tllm"][0]["tok_per_s"])
+    if r > 0:
+        print(f"decode tok/s: reference kernels {r:.1f}, libtllm_b200 {t:.1f}  ({t / r:.2f}x); "
+              f"prefill ms: {res['engine_ref'][0]['prefill_ms']} vs {res['engine_tllm'][0]['prefill_ms']}")
+
+
+if __name__ == "__main__":
+    main()
