@@ -141,8 +141,8 @@ int tllm_b200_weight_unpack(const void* packed, int rows, int cols, int group_si
 /*
  * Associates a prepared buffer with the reference arrays it was made from, keyed
  * by the nonzero_masks pointer: afterwards tllm_b200_gemv, _gemv_batched,
- * _gemv_int8 and (for M <= TLLM_MAX_BATCH) _gemm called with that pointer and the
- * same rows/cols use the prepared weights, so the reference's call sites
+ * _gemv_int8 and _gemm called with that pointer and the same rows/cols use the
+ * prepared weights, so the reference's call sites
  * (src/transformer.cpp:102-143,199-217,264-278) need no change.  Unregister
  * before freeing either buffer (reference Model::free_gpu, src/model.cpp:221-250).
  */
@@ -211,9 +211,9 @@ int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y,
 
 /*
  * Prefill GEMM on prepared weights: C[M,N] = A[M,K] . W^T, same contract as
- * tllm_b200_gemm.  M > TLLM_MAX_BATCH runs the tcgen05 tensor-core kernel (weights
- * expanded to exact FP16 {-s,0,+s} in tensor memory, FP32 accumulation in TMEM);
- * smaller M runs the batched GEMV.  tllm_b200_gemm reaches the same kernels when
+ * tllm_b200_gemm.  M > 6 runs the tcgen05 tensor-core kernel (weights expanded to
+ * exact FP16 {-s,0,+s} in tensor memory, FP32 accumulation in TMEM; token tile 32, 64,
+ * 128 or 256 by M); smaller M runs passes of the streaming GEMV.  tllm_b200_gemm reaches the same kernels when
  * the weight pointer has been registered.
  */
 int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int N, int K, void* stream);

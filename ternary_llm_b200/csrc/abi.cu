@@ -45,6 +45,9 @@ static int check_device()
     return TLLM_OK;
 }
 
+// Largest token count served by passes of the streaming GEMV; above it the tcgen05 kernel.
+constexpr int kGemvMaxBatch = 6;
+
 static inline bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 static int check_weights(const void* nz, const void* sg, const void* scales, int rows, int cols, int gs)
@@ -97,8 +100,14 @@ int tllm_b200_gemv_batched(const uint32_t* nz, const uint32_t* sg, const void* s
     if (misaligned(x, 16)) return fail(TLLM_ERR_ALIGN, "activation pointer must be 16-byte aligned");
     if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
     if ((st = check_device())) return st;
-    if (const uint8_t* packed = lookup_packed(nz, rows, cols))
+    if (const uint8_t* packed = lookup_packed(nz, rows, cols)) {
+        // up to six vectors: the streaming GEMV (two share one weight pass); more: the
+        // tensor-core kernel with a 32-token tile reads the weights once for the whole batch
+        // (measured cross-over on the 8B shapes)
+        if (batch > kGemvMaxBatch && gemm_tcgen05_supported(batch, rows, cols))
+            return launch_gemm_tcgen05((const half*)x, packed, (half*)y, batch, rows, cols, (cudaStream_t)stream);
         return launch_gemv_packed(packed, (const half*)x, (half*)y, batch, rows, cols, (cudaStream_t)stream);
+    }
     return launch_gemv_simt(nz, sg, (const half*)scales, (const half*)x, (half*)y, batch, rows, cols,
                             (cudaStream_t)stream);
 }
@@ -147,7 +156,7 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B, 
     if ((st = check_device())) return st;
     // Token blocks of at most kMaxBatch rows, each one pass over the weights.
     const uint8_t* packed = lookup_packed(nz_B, N, K);
-    if (packed && M > kMaxBatch && gemm_tcgen05_supported(M, N, K))
+    if (packed && M > kGemvMaxBatch && gemm_tcgen05_supported(M, N, K))
         return launch_gemm_tcgen05((const half*)A, packed, (half*)C, M, N, K, (cudaStream_t)stream);
     for (int m0 = 0; m0 < M; m0 += kMaxBatch) {
         const int b = (M - m0 < kMaxBatch) ? (M - m0) : kMaxBatch;
@@ -222,6 +231,8 @@ int tllm_b200_gemv_packed(const void* packed, const void* x, void* y, int batch,
     int st = check_packed_call(packed, x, y, rows, cols);
     if (st) return st;
     if (batch < 1 || batch > kMaxBatch) return fail(TLLM_ERR_BATCH, "batch %d outside 1..%d", batch, kMaxBatch);
+    if (batch > kGemvMaxBatch && gemm_tcgen05_supported(batch, rows, cols))
+        return launch_gemm_tcgen05((const half*)x, (const uint8_t*)packed, (half*)y, batch, rows, cols, (cudaStream_t)stream);
     return launch_gemv_packed((const uint8_t*)packed, (const half*)x, (half*)y, batch, rows, cols, (cudaStream_t)stream);
 }
 
@@ -277,7 +288,7 @@ int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int
     if (misaligned(C, 2)) return fail(TLLM_ERR_ALIGN, "C must be 2-byte aligned");
     int st = check_device();
     if (st) return st;
-    if (M <= kMaxBatch)
+    if (M <= kGemvMaxBatch)
         return launch_gemv_packed((const uint8_t*)packed, (const half*)A, (half*)C, M, N, K, (cudaStream_t)stream);
     return launch_gemm_tcgen05((const half*)A, (const uint8_t*)packed, (half*)C, M, N, K, (cudaStream_t)stream);
 }

@@ -33,17 +33,25 @@ namespace tllm {
 namespace gemm {
 
 constexpr int kTileN = 128;          // output features per CTA (MMA M, TMEM lanes)
-constexpr int kTileM = 256;          // tokens per CTA (MMA N)
 constexpr int kStageK = 128;         // K per pipeline stage = one scale group
-constexpr int kBStages = 3;          // activation stages in shared memory
 constexpr int kAStages = 2;          // weight stages in tensor memory
 constexpr int kBoxK = 64;            // TMA box inner extent (128 bytes of FP16)
-constexpr int kBoxBytes = kTileM * kBoxK * 2;          // 32 KB
-constexpr int kStageBytes = 2 * kBoxBytes;             // 64 KB
 constexpr int kThreads = 256;
-constexpr int kAccCols = kTileM;     // 256 FP32 accumulator columns
 constexpr int kAColsPerStage = kStageK / 2;            // 64 columns of FP16 pairs
-constexpr int kTmemCols = 512;
+
+// Per token-tile size TM (tokens per CTA = MMA N): 256 for long prefills; 128/64/32 for
+// short ones and for decode batches, where two CTAs share an SM (half the shared memory
+// and half the tensor memory each) so that twice as many warps expand weights.
+template <int TM>
+struct Cfg {
+    static constexpr int kBoxBytes = TM * kBoxK * 2;
+    static constexpr int kStageBytes = 2 * kBoxBytes;                    // TM x 128 K x FP16
+    static constexpr int kBStages = (TM == 256) ? 3 : (TM == 128) ? 3 : (TM == 64) ? 6 : 8;
+    static constexpr int kAccCols = TM;                                  // FP32 accumulator columns
+    static constexpr int kTmemCols = (TM == 256) ? 512 : 256;            // power of two >= TM + 128
+    static constexpr int kCtasPerSm = (TM == 256) ? 1 : 2;
+    static constexpr size_t kSmem = (size_t)kBStages * kStageBytes + 1024;
+};
 
 // PRMT tables: pair code -> FP16 high byte (+1 -> 0x3C, -1 -> 0xBC, 0 -> 0x00).
 // index:            0     1     2     3     4     5     6     7
@@ -112,13 +120,14 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
 }
 
 // kind::f16 instruction descriptor: FP16 x FP16 -> FP32, both operands K-major.
+template <int TM>
 __device__ __forceinline__ uint32_t make_idesc()
 {
     uint32_t d = 0;
     d |= 1u << 4;                          // D format F32
     d |= 0u << 7;                          // A format F16
     d |= 0u << 10;                         // B format F16
-    d |= (uint32_t)(kTileM >> 3) << 17;    // N
+    d |= (uint32_t)(TM >> 3) << 17;        // N
     d |= (uint32_t)(kTileN >> 4) << 24;    // M
     return d;
 }
@@ -169,9 +178,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
                  : "r"(taddr) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int TM>
+__global__ void __launch_bounds__(kThreads, Cfg<TM>::kCtasPerSm)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
 {
+    constexpr int kBStages = Cfg<TM>::kBStages, kStageBytes = Cfg<TM>::kStageBytes, kBoxBytes = Cfg<TM>::kBoxBytes;
+    constexpr int kAccCols = Cfg<TM>::kAccCols, kTmemCols = Cfg<TM>::kTmemCols, kTileM = TM;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the 128-byte swizzle atoms
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -231,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = make_idesc();
+            const uint32_t idesc = make_idesc<TM>();
             for (int it = 0; it < nstages; it++) {
                 const int sb = it % kBStages, sa = it % kAStages;
                 if (!mbar_wait(full_b(sb), (it / kBStages) & 1, abortp) ||
@@ -361,22 +373,37 @@ bool gemm_tcgen05_supported(int M, int N, int K)
     return M >= 1 && K >= gemm::kStageK && K % gemm::kStageK == 0;
 }
 
+template <int TM>
+static int launch_tm(gemm::EncodeTiledFn enc, const half* A, const gemm::Args& a, cudaStream_t stream)
+{
+    using namespace gemm;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * sizeof(half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kBoxK, (cuuint32_t)TM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TLLM_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr[dev]) {
+        cudaFuncSetAttribute(gemm_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<TM>::kSmem);
+        attr[dev] = true;
+    }
+    const dim3 grid((a.N + kTileN - 1) / kTileN, (a.M + TM - 1) / TM);
+    gemm_kernel<TM><<<grid, kThreads, Cfg<TM>::kSmem, stream>>>(map, a);
+    return check_launch("gemm_tcgen05");
+}
+
 // A: half [M,K] row-major (16-byte aligned), packed: prepared weights of [N,K], C: half [M,N].
 int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, int N, int K, cudaStream_t stream)
 {
     using namespace gemm;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(TLLM_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(half)};
-    const cuuint32_t box[2] = {(cuuint32_t)kBoxK, (cuuint32_t)kTileM};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(A), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(TLLM_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
-
     int* err = device_error_flag();
     if (!err) return fail(TLLM_ERR_LAUNCH, "device scratch unavailable");
     Args a;
@@ -388,17 +415,11 @@ int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, in
     a.groups = K / kStageK;
     a.nrb = (N + 15) / 16;
     a.err = err;
-    const size_t smem = (size_t)kBStages * kStageBytes + 1024;
-    static bool attr[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr[dev]) {
-        cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr[dev] = true;
-    }
-    const dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
-    gemm_kernel<<<grid, kThreads, smem, stream>>>(map, a);
-    return check_launch("gemm_tcgen05");
+    // token tile: the smallest that holds M, 256 for long prefills
+    if (M <= 32) return launch_tm<32>(enc, A, a, stream);
+    if (M <= 64) return launch_tm<64>(enc, A, a, stream);
+    if (M <= 128) return launch_tm<128>(enc, A, a, stream);
+    return launch_tm<256>(enc, A, a, stream);
 }
 
 }  // namespace tllm
