@@ -144,17 +144,28 @@ def cpu_layer_sample(reps: int, threads: int):
 
 
 def run_reference(args):
+    """The reference's CPU implementation of the path on the host cores: its scalar matvec
+    over one layer of the arm's workload per step (8B shapes at N = 1, the 70B shapes of the
+    tensor-parallel arm at N > 1).  Under torchrun only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    # each step = one layer's seven GEMVs (1/32 of the GPU arm's step)
     from oracle import cpu
     from ternary_llm_b200 import pack
     kind = "reference" if cpu.have_ref() else "port"
+    if args.gpus > 1:
+        shapes = [("q", 8192, 8192), ("k", 1024, 8192), ("v", 1024, 8192), ("o", 8192, 8192),
+                  ("gate", 28672, 8192), ("up", 28672, 8192), ("down", 8192, 28672)]
+        metric, n_layers = "ternary_gemv_hbm_throughput_llama70b_shapes_tp_batch1", 80
+        workload = "LLaMA-70B-shape ternary projection stack, batch 1, CPU scalar matvec"
+    else:
+        shapes, metric, n_layers = SHAPES_8B, METRIC, LAYERS_8B
+        workload = "llama3-8b projection shapes, batch 1, CPU scalar matvec"
+    layer_bytes = sum(gemv_bytes(n, k) for _, n, k in shapes)
     mats = []
     rng = np.random.default_rng(0)
-    for i, (_, n, k) in enumerate(SHAPES_8B):
+    for i, (_, n, k) in enumerate(shapes):
         nz, sg, sc = pack.random_ternary_weight(n, k, seed=1000 + i)
         mats.append((nz, sg, sc.astype(np.float32), rng.standard_normal(k).astype(np.float16).astype(np.float32)))
 
@@ -168,13 +179,13 @@ def run_reference(args):
     for _ in range(args.steps):
         step()
     dt = (time.perf_counter() - t0) / args.steps
-    val = LAYER_BYTES / dt / 1e9
-    sample = "one layer (7 GEMVs, 57.9 MB of packed weights) per step = 1/32 of the GPU arm's step"
+    val = layer_bytes / dt / 1e9
+    sample = f"one layer (7 GEMVs, {layer_bytes / 1e6:.1f} MB of packed weights) per step = 1/{n_layers} of the GPU arm's step"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama3-8b projection shapes, batch 1, CPU scalar matvec", "sample": sample},
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "sample": sample},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -17,6 +17,8 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
+# Where a checkout of the reference project is looked for (optional; only build steps use it).
+REF_DIR = os.environ.get("TLLM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 _PORT = os.path.join(_HERE, "liboracle_cpu.so")
 _REF = os.path.join(_HERE, "_ref", "libref.so")
 
@@ -26,7 +28,7 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 _i8p = ctypes.POINTER(ctypes.c_int8)
 
 
-def build(ref_dir: str | None = "/root/reference") -> None:
+def build(ref_dir: str | None = REF_DIR) -> None:
     """Compile the C restatement, and the reference's own sources when they are
     present on this machine."""
     subprocess.check_call(["make", "-s", "-C", _HERE])

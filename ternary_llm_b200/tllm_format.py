@@ -230,9 +230,10 @@ def load_projections(path: str, device, register: bool = False):
         for name in PROJ_NAMES:
             t = layer[name]
             rows, cols = t.shape
-            nz = torch.from_numpy(np.ascontiguousarray(t.nonzero_masks).view(np.int32)).to(device)
-            sg = torch.from_numpy(np.ascontiguousarray(t.sign_masks).view(np.int32)).to(device)
-            sc = torch.from_numpy(np.ascontiguousarray(t.scales)).to(device)
+            # copies: the file views are read-only memory maps
+            nz = torch.from_numpy(np.array(t.nonzero_masks).view(np.int32)).to(device)
+            sg = torch.from_numpy(np.array(t.sign_masks).view(np.int32)).to(device)
+            sc = torch.from_numpy(np.array(t.scales)).to(device)
             d[name] = ops.PreparedWeight(nz, sg, sc, rows, cols, register=register, keep_source=register)
         out.append(d)
     return m.config, out

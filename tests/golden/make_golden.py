@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerate the golden fixtures from the reference project itself.
 
-Needs a checkout of jastaq/ternary-llm (default /root/reference) and
+Needs a checkout of jastaq/ternary-llm (--ref, default oracle.cpu.REF_DIR) and
 oracle/_ref/libref.so (make -C oracle ref).  It imports the reference's own
 ternarize/pack.py for the packing fixtures and calls the reference's compiled
 cpu_reference (tests/test_ternary_gemv.cu:40-75) for the matvec fixtures, so the
@@ -23,8 +23,9 @@ sys.path.insert(0, ROOT)
 
 
 def main():
+    from oracle.cpu import REF_DIR
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=REF_DIR)
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "ternarize"))
     sys.path.insert(0, os.path.join(args.ref, "tests"))

@@ -8,7 +8,10 @@ import sys
 import numpy as np
 import pytest
 
+from oracle.cpu import REF_DIR
 from ternary_llm_b200 import tllm_format as tf
+
+DIAGNOSE = os.path.join(REF_DIR, "tools", "diagnose_format.py")
 
 CFG = tf.TllmConfig(vocab_size=320, hidden_dim=256, intermediate_dim=512, n_layers=2, n_heads=4,
                     n_kv_heads=2, head_dim=64, max_seq_len=128, rope_theta=500000.0, rms_norm_eps=1e-5)
@@ -64,14 +67,14 @@ def test_truncated_file_is_rejected(tmp_path):
         tf.read_tllm(path)
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/tools/diagnose_format.py"),
+@pytest.mark.skipif(not os.path.exists(DIAGNOSE),
                     reason="reference checkout not present")
 def test_reference_offset_checker_accepts_the_file(tmp_path):
     m = tf.random_model(CFG, seed=2)
     m.tokenizer = b"x" * 100
     path = str(tmp_path / "m.tllm")
     tf.write_tllm(path, m)
-    out = subprocess.run([sys.executable, "/root/reference/tools/diagnose_format.py", path],
+    out = subprocess.run([sys.executable, DIAGNOSE, path],
                          capture_output=True, text=True, check=True).stdout
     assert "MISMATCH" not in out and "Looks valid" in out
     assert "Tokenizer size at expected position: 100 bytes" in out
