@@ -986,6 +986,10 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     // split at tile granularity (K is split across CTAs).
     const int per_cta_rb = (nrb + grid - 1) / grid;
     a.aligned = (nrb >= grid && (double)nrb / ((double)per_cta_rb * grid) >= 0.8) ? 1 : 0;
+    // Fewer row blocks than SMs and short rows (one ring slot per warp at most): such a
+    // matrix is a few hundred KB, latency-bound, and the cross-CTA combine would cost more
+    // than the idle SMs; one CTA per row block.
+    if (nrb < grid && a.groups <= kWarps * kSlotTiles) a.aligned = 1;
     const int items = a.aligned ? nrb : tiles;
     if (items < grid) grid = items;
     a.part_q = items / grid;
@@ -1210,6 +1214,10 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     int grid = nd.sms < kMaxCtas ? nd.sms : kMaxCtas;
     const int per_cta_rb = (nrb + grid - 1) / grid;
     a.aligned = (nrb >= grid && (double)nrb / ((double)per_cta_rb * grid) >= 0.8) ? 1 : 0;
+    // Fewer row blocks than SMs and short rows (one ring slot per warp at most): such a
+    // matrix is a few hundred KB, latency-bound, and the cross-CTA combine would cost more
+    // than the idle SMs; one CTA per row block.
+    if (nrb < grid && a.groups <= kWarps * kSlotTiles) a.aligned = 1;
     const int items = a.aligned ? nrb : tiles;
     if (items < grid) grid = items;
     a.part_q = items / grid;
