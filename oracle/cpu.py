@@ -77,6 +77,16 @@ def ref():
         lib.ref_ternary_gemv_int8.argtypes = [vp] * 4 + [ctypes.c_float, vp] + [ctypes.c_int] * 3 + [vp]
         lib.ref_quantize_absmax_int8.argtypes = [vp] * 3 + [ctypes.c_int, vp]
         lib.ref_ternary_gemm.argtypes = [vp] * 5 + [ctypes.c_int] * 4 + [vp]
+        i, f = ctypes.c_int, ctypes.c_float
+        lib.ref_rmsnorm_forward.argtypes = [vp] * 5 + [i, i, f, vp]
+        lib.ref_rope_forward.argtypes = [vp, vp] + [i] * 6 + [f, vp]
+        lib.ref_attention_forward.argtypes = [vp] * 4 + [i] * 7 + [vp]
+        lib.ref_silu_mul_forward.argtypes = [vp] * 3 + [i, vp]
+        lib.ref_add_forward.argtypes = [vp] * 3 + [i, vp]
+        lib.ref_embedding_lookup.argtypes = [vp] * 3 + [i, i, vp]
+        lib.ref_copy_to_kv_cache.argtypes = [vp] * 4 + [i] * 6 + [vp]
+        lib.ref_fp16_gemv.argtypes = [vp] * 3 + [i, i, vp]
+        lib.ref_fp16_gemm.argtypes = [vp] * 3 + [i] * 3 + [vp]
         _ref = lib
     return _ref
 

@@ -30,7 +30,7 @@ int check_launch(const char* what)
 }
 
 // The kernels are built for sm_100a only; refuse any other device loudly.
-static int check_device()
+int check_device()
 {
     static int ok[64] = {};   // 0 unknown, 1 good, -1 bad
     int dev = -1;

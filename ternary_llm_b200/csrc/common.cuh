@@ -15,6 +15,8 @@ constexpr int kMaxBatch = TLLM_MAX_BATCH;
 int fail(int status, const char* fmt, ...);
 // cudaPeekAtLastError -> status (does not clear sticky errors, does not sync).
 int check_launch(const char* what);
+// TLLM_OK when the current device is compute capability 10.x, else TLLM_ERR_DEVICE.
+int check_device();
 
 // ---- launchers implemented in the kernel translation units ----------------
 // General-shape SIMT kernels on the reference layout (any rows >= 1).
@@ -46,6 +48,8 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
                                  cudaStream_t stream);
 int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
                              const half* x, cudaStream_t stream);
+int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows,
+                                  int cols, const int8_t* xq, const float* scale_dev, cudaStream_t stream);
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream);
 

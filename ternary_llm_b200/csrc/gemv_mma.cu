@@ -62,6 +62,7 @@ struct GemvArgs {
     const void* x;          // half [batch, cols] or int8 [cols]
     half* y;                // half [batch, rows]
     float in_scale;         // INT8 mode: activation scale
+    const float* in_scale_dev;  // INT8 mode: when not null the scale is read from device memory instead
     int rows, cols, groups; // groups = cols / 128 = tiles per row block
     int batch;              // 1 or 2 vectors handled by this launch
     int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
@@ -455,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
 
     // ---- reduction: warps of this CTA, then CTAs, row block by row block -----------
     const int nb = (MODE == kF16B2) ? a.batch : 1;
-    const float oscale = I8 ? a.in_scale : 1.0f;
+    const float oscale = I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f;
     float* myrec = a.ws + (size_t)blockIdx.x * 64;
 
     if (a.ar_world > 0) {
@@ -579,6 +580,7 @@ struct CwArgs {
     int count;                      // matrices in this launch
     const void* x;                  // half [cols] or int8 [cols], shared by all matrices
     float in_scale;
+    const float* in_scale_dev;      // INT8 mode: scale in device memory when not null
     int cols, groups;
     int part_q, part_r;     // row blocks = gridDim.x * part_q + part_r
     int gpw;                // groups per warp, ceil(groups / kWarps)
@@ -776,7 +778,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_cw_kernel(const CwA
     PHASE(5);
 
     // ---- add the warps' partial sums in warp order and store -------------------------
-    const float oscale = I8 ? a.in_scale : 1.0f;
+    const float oscale = I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f;
     const int nwarps_used = min(kWarps, G);
     for (int rbl = warp; rbl < nrb; rbl += kWarps) {
         if ((lane & 1) == 0) {
@@ -961,7 +963,7 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
 
 // x: half [batch, cols] (mode f16) or int8 [cols]; batch 1..2 per launch.
 static int launch_packed_once(const uint8_t* packed, const void* x, half* y, float in_scale, int mode,
-                              int batch, int rows, int cols, cudaStream_t stream)
+                              int batch, int rows, int cols, cudaStream_t stream, const float* in_scale_dev = nullptr)
 {
     DeviceScratch* s = nullptr;
     int st = get_scratch(&s);
@@ -971,6 +973,7 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.x = x;
     a.y = y;
     a.in_scale = in_scale;
+    a.in_scale_dev = in_scale_dev;
     a.rows = rows;
     a.cols = cols;
     a.groups = cols / kGroup;
@@ -1067,7 +1070,8 @@ static int launch_cw_t(const CwArgs& a, int grid, size_t smem, cudaStream_t stre
 }
 
 static int launch_cw_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, const void* x,
-                           float in_scale, int mode, int cols, int sms, cudaStream_t stream)
+                           float in_scale, int mode, int cols, int sms, cudaStream_t stream,
+                           const float* in_scale_dev = nullptr)
 {
     CwArgs a = {};
     int nrb = 0;
@@ -1082,6 +1086,7 @@ static int launch_cw_multi(int count, const uint8_t* const* packed, half* const*
     a.count = count;
     a.x = x;
     a.in_scale = in_scale;
+    a.in_scale_dev = in_scale_dev;
     a.cols = cols;
     a.groups = cols / kGroup;
     const int grid = sms < kMaxCtas ? sms : kMaxCtas;
@@ -1108,12 +1113,14 @@ static int launch_cw_multi(int count, const uint8_t* const* packed, half* const*
 
 // Several matrices that share x and the column count (q/k/v; gate/up) in one launch when
 // together they fill the SMs; otherwise one launch each.
-int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
-                             const half* x, cudaStream_t stream)
+// x is FP16 (xq == nullptr) or INT8 with its scale in device memory.
+static int gemv_packed_multi_any(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
+                                 const half* x, const int8_t* xq, const float* scale_dev, cudaStream_t stream)
 {
     DeviceScratch* s = nullptr;
     int st = get_scratch(&s);
     if (st) return st;
+    const bool i8 = (xq != nullptr);
     // One fused launch pays off when some matrix alone cannot fill the SMs with whole row
     // blocks (k and v of grouped-query attention); matrices that can are streamed one by
     // one by the general kernel, which is the faster of the two for them.
@@ -1124,12 +1131,32 @@ int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* cons
         small = small || !cw_eligible(s->sms, rows[i], cols);
     }
     if (small && count >= 2 && count <= kMaxFused && cw_eligible_rb(s->sms, nrb, cols)) {
-        st = launch_cw_multi(count, packed, y, rows, x, 1.0f, kF16B1, cols, s->sms, stream);
+        st = launch_cw_multi(count, packed, y, rows, i8 ? (const void*)xq : (const void*)x, 1.0f,
+                             i8 ? kI8 : kF16B1, cols, s->sms, stream, scale_dev);
         if (st != TLLM_ERR_SIZE) return st;
     }
-    for (int i = 0; i < count; i++)
-        if ((st = launch_gemv_packed(packed[i], x, y[i], 1, rows[i], cols, stream))) return st;
+    for (int i = 0; i < count; i++) {
+        st = i8 ? launch_packed_once(packed[i], xq, y[i], 1.0f, kI8, 1, rows[i], cols, stream, scale_dev)
+                : launch_gemv_packed(packed[i], x, y[i], 1, rows[i], cols, stream);
+        if (st) return st;
+    }
     return TLLM_OK;
+}
+
+// Several matrices that share x and the column count (q/k/v; gate/up) in one launch when
+// together they fill the SMs; otherwise one launch each.
+int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
+                             const half* x, cudaStream_t stream)
+{
+    return gemv_packed_multi_any(count, packed, y, rows, cols, x, nullptr, nullptr, stream);
+}
+
+// The same for INT8 activations whose scale stays in device memory (written by the
+// quantiser that ran before on the stream), so that no host read sits between the two.
+int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows,
+                                  int cols, const int8_t* xq, const float* scale_dev, cudaStream_t stream)
+{
+    return gemv_packed_multi_any(count, packed, y, rows, cols, nullptr, xq, scale_dev, stream);
 }
 
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
