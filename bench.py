@@ -591,7 +591,8 @@ def run_ours(args):
 
 def run_case(args):
     """A small single-kernel case for profilers: `gemv:NxK[:copies]`, `gemv_int8:NxK[:copies]`
-    or `gemm:MxNxK`.  Distinct matrices are cycled so that the weights come from HBM."""
+    `gemm:MxNxK`, or `decode:ARCH[:prompt[:steps[:eager]]]` (the decoder on a random model).
+    Distinct matrices are cycled so that the weights come from HBM."""
     import torch
 
     import ternary_llm_b200 as tl
@@ -623,6 +624,44 @@ def run_case(args):
         c = torch.zeros(m, n, device=dev, dtype=torch.float16)
         for _ in range(4):
             tl.ternary_gemm_packed(a, w, c, m)
+    elif kind == "decode":
+        # decode:ARCH[:prompt[:steps[:eager]]] -- the library's decoder on a seeded random model of
+        # the benchmark's 1B architecture (`1b`, 16 layers) or a 4-layer cut of it (`1b-4l`)
+        from ternary_llm_b200 import tllm_format as tf
+        arch = dict(vocab_size=128256, hidden_dim=2048, intermediate_dim=8192, n_layers=16, n_heads=32, n_kv_heads=8,
+                    head_dim=64, max_seq_len=1024, rope_theta=500000.0, rms_norm_eps=1e-5)
+        if dims == "1b-4l":
+            arch.update(n_layers=4, vocab_size=32000)
+        elif dims != "1b":
+            raise SystemExit(f"unknown decode architecture {dims}")
+        n_prompt = int(rest[0]) if len(rest) > 0 else 512
+        n_steps = int(rest[1]) if len(rest) > 1 else 128
+        eager = len(rest) > 2 and rest[2] == "eager"
+        cfg = tf.TllmConfig(**arch)
+        dec = tl.Decoder(tf.random_model(cfg, seed=2026), int8_decode=True)
+        prompt = torch.from_numpy(np.random.default_rng(0).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)).to(dev)
+        logits = dec.forward(prompt, 0)
+        first = int(logits.float().argmax().item())
+        info = {}
+        if eager:
+            tok = first
+            for i in range(n_steps):
+                lg = dec.forward(torch.tensor([tok], dtype=torch.int32, device=dev), n_prompt + i)
+                tok = int(lg.float().argmax().item())
+        else:
+            dec.generate(first, n_prompt, min(4, n_steps))
+            dec.reset()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dec.forward(prompt, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            toks, ms = dec.generate(first, n_prompt, n_steps)
+            info = {"prefill_ms": e0.elapsed_time(e1), "decode_ms_per_token": ms, "tok_per_s": 1e3 / ms}
+        torch.cuda.synchronize()
+        tl.check_device_errors()
+        print(json.dumps({"case": args.case, "status": "ok", **info}))
+        return
     else:
         raise SystemExit(f"unknown case {args.case}")
     torch.cuda.synchronize()
@@ -642,7 +681,7 @@ def main():
                     help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
-                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemm:MxNxK")
+                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]]")
     args = ap.parse_args()
     if args.case:
         return run_case(args)

@@ -11,11 +11,16 @@
 //
 // One CTA serves one KV head and ALL the query heads that share it, so K and V are read
 // once per group instead of once per query head.  The CTA walks its range of cache
-// positions in chunks of 256 with an online softmax:
+// positions in chunks of 256 with an online softmax.  A chunk of K and of V is one
+// contiguous block of the cache ([position][head_dim]); each is brought into shared
+// memory by a single bulk copy (cp.async.bulk, completion on an mbarrier, bounded wait),
+// so the whole chunk is in flight at once instead of one dependent load per position:
 //   scores  - one thread per position, dot products against the group's query heads
-//             (queries pre-scaled in shared memory), 128-bit K loads;
+//             (queries pre-scaled in shared memory); the 16-byte pieces of a row are
+//             visited in an order rotated by the position, which keeps the eight lanes
+//             of a shared-memory phase on different banks;
 //   softmax - one warp per query head over the chunk's 256 scores;
-//   P.V     - one thread per (query head, channel), V rows read coalesced.
+//   P.V     - one thread per (query head, channel), V rows read from shared memory.
 // Decode (seq_len == 1) splits the cache positions over several CTAs (one chunk each);
 // each writes (max, sum, unnormalised output) and the CTA that arrives last on a counter
 // merges them in split order and resets the counter, so replays of a captured graph need
@@ -32,6 +37,21 @@ constexpr int kAttnChunk = 256;       // cache positions per pass = per decode s
 constexpr int kAttnMaxGroup = 16;     // query heads per KV head
 constexpr int kAttnMaxElems = 16;     // outputs per thread: group * head_dim / 256
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Bounded wait on an mbarrier phase (about a second at most); false = gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+#pragma unroll 1
+    for (int i = 0; i < (1 << 22); i++) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 struct AttnArgs {
     const half* q;
     const half* k_cache;
@@ -42,6 +62,7 @@ struct AttnArgs {
     int nsplit;                // decode: CTAs per (batch, kv head); 1 otherwise
     float* ws;                 // [batch * n_kv_heads][nsplit][group * (head_dim + 2)]
     unsigned* counters;        // [batch * n_kv_heads]
+    int* err;                  // device error flag (set when a bounded wait gives up)
 };
 
 __global__ void __launch_bounds__(kAttnThreads)
@@ -57,12 +78,22 @@ attention_kernel(const AttnArgs a)
     const int s_idx = decode ? 0 : blockIdx.x;
     const int split = decode ? blockIdx.x : 0;
 
-    float* qs = smem;                         // [G][hd] queries times 1/sqrt(hd)
+    half* ks = reinterpret_cast<half*>(smem);                 // [kAttnChunk][hd] K chunk
+    half* vs = ks + kAttnChunk * hd;                          // [kAttnChunk][hd] V chunk
+    float* qs = reinterpret_cast<float*>(vs + kAttnChunk * hd);   // [G][hd] queries times 1/sqrt(hd)
     float* ps = qs + G * hd;                  // [G][kAttnChunk] scores, then probabilities
     float* m_run = ps + G * kAttnChunk;       // [G] running maximum
     float* l_run = m_run + kAttnMaxGroup;     // [G] running sum
     float* corr = l_run + kAttnMaxGroup;      // [G] rescale factor of this chunk
     __shared__ int s_last;
+    __shared__ int s_ok;
+    __shared__ __align__(8) unsigned long long s_bar;
+    const uint32_t bar = smem_u32(&s_bar);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
 
     pdl_wait();
     int kv_len = a.kv_len;
@@ -94,16 +125,36 @@ attention_kernel(const AttnArgs a)
     for (int e = 0; e < kAttnMaxElems; e++) o[e] = 0.f;
     __syncthreads();
 
+    uint32_t phase = 0;
     for (int c0 = lo; c0 < hi; c0 += kAttnChunk) {
         const int nc = min(kAttnChunk, hi - c0);
+        // ---- stage the chunk: one bulk copy each for K and V -----------------------
+        if (tid == 0) {
+            const uint32_t bytes = (uint32_t)nc * hd * sizeof(half);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(ks)), "l"(kb + (size_t)c0 * hd), "r"(bytes), "r"(bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(vs)), "l"(vb + (size_t)c0 * hd), "r"(bytes), "r"(bar) : "memory");
+            s_ok = mbar_wait_bounded(bar, phase) ? 1 : 0;
+        }
+        phase ^= 1u;
+        __syncthreads();
+        if (!s_ok) {                       // uniform: the copy never completed
+            if (tid == 0 && a.err) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+            return;
+        }
         // ---- scores: thread j <-> position c0 + j --------------------------------
         if (tid < nc) {
             float dot[kAttnMaxGroup];
 #pragma unroll
             for (int g = 0; g < kAttnMaxGroup; g++) dot[g] = 0.f;
-            const uint4* k4 = reinterpret_cast<const uint4*>(kb + (size_t)(c0 + tid) * hd);
-            for (int d8 = 0; d8 < hd / 8; d8++) {
-                const uint4 raw = __ldg(k4 + d8);
+            const uint4* k4 = reinterpret_cast<const uint4*>(ks + (size_t)tid * hd);
+            const int nd8 = hd >> 3;
+            for (int i8 = 0; i8 < nd8; i8++) {
+                int d8 = i8 + tid;
+                d8 -= (d8 / nd8) * nd8;                    // (i8 + tid) % nd8
+                const uint4 raw = k4[d8];
                 const half2* h = reinterpret_cast<const half2*>(&raw);
                 float kf[8];
 #pragma unroll
@@ -158,21 +209,17 @@ attention_kernel(const AttnArgs a)
                 if (idx < G * hd) {
                     const int g = idx / hd, d = idx - g * hd;
                     const float* p = ps + g * kAttnChunk;
-                    const half* vp = vb + (size_t)c0 * hd + d;
-                    float acc = o[e] * corr[g];
+                    const half* vp = vs + d;
+                    float acc0 = o[e] * corr[g], acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
                     int j = 0;
                     for (; j + 4 <= nc; j += 4) {
-                        const float v0 = __half2float(vp[(size_t)(j + 0) * hd]);
-                        const float v1 = __half2float(vp[(size_t)(j + 1) * hd]);
-                        const float v2 = __half2float(vp[(size_t)(j + 2) * hd]);
-                        const float v3 = __half2float(vp[(size_t)(j + 3) * hd]);
-                        acc = fmaf(p[j], v0, acc);
-                        acc = fmaf(p[j + 1], v1, acc);
-                        acc = fmaf(p[j + 2], v2, acc);
-                        acc = fmaf(p[j + 3], v3, acc);
+                        acc0 = fmaf(p[j], __half2float(vp[(j + 0) * hd]), acc0);
+                        acc1 = fmaf(p[j + 1], __half2float(vp[(j + 1) * hd]), acc1);
+                        acc2 = fmaf(p[j + 2], __half2float(vp[(j + 2) * hd]), acc2);
+                        acc3 = fmaf(p[j + 3], __half2float(vp[(j + 3) * hd]), acc3);
                     }
-                    for (; j < nc; j++) acc = fmaf(p[j], __half2float(vp[(size_t)j * hd]), acc);
-                    o[e] = acc;
+                    for (; j < nc; j++) acc0 = fmaf(p[j], __half2float(vp[j * hd]), acc0);
+                    o[e] = (acc0 + acc1) + (acc2 + acc3);
                 }
             }
         }
@@ -256,8 +303,9 @@ int launch_attention(const half* q, const half* k_cache, const half* v_cache, ha
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(TLLM_ERR_SHAPE, "attention: n_heads=%d n_kv_heads=%d", n_heads, n_kv_heads);
     const int G = n_heads / n_kv_heads;
     if (G > kAttnMaxGroup) return fail(TLLM_ERR_SHAPE, "attention: %d query heads per KV head (limit %d)", G, kAttnMaxGroup);
-    if (head_dim % 8 || G * head_dim > kAttnMaxElems * kAttnThreads)
-        return fail(TLLM_ERR_SHAPE, "attention: head_dim=%d with %d heads per group is not supported", head_dim, G);
+    if (head_dim % 8 || head_dim > 128 || G * head_dim > kAttnMaxElems * kAttnThreads)
+        return fail(TLLM_ERR_SHAPE, "attention: head_dim=%d (a multiple of 8 up to 128) with %d heads per group is not supported",
+                    head_dim, G);
     if (!kv_len_dev && (kv_len < seq_len || kv_len > kv_len_max))
         return fail(TLLM_ERR_SHAPE, "attention: kv_len=%d seq_len=%d kv_len_max=%d", kv_len, seq_len, kv_len_max);
     AttnArgs a = {};
@@ -276,12 +324,14 @@ int launch_attention(const half* q, const half* k_cache, const half* v_cache, ha
     a.counters = counters;
     const bool decode = (seq_len == 1);
     a.nsplit = (decode && ws) ? (kv_len_max + kAttnChunk - 1) / kAttnChunk : 1;
-    const size_t smem = ((size_t)G * head_dim + (size_t)G * kAttnChunk + 3 * kAttnMaxGroup) * sizeof(float);
+    a.err = device_error_flag();
+    const size_t smem = (size_t)2 * kAttnChunk * head_dim * sizeof(half) +
+                        ((size_t)G * head_dim + (size_t)G * kAttnChunk + 3 * kAttnMaxGroup) * sizeof(float);
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr[dev]) {
-        cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr[dev] = true;
     }
     const dim3 grid(decode ? a.nsplit : seq_len, n_kv_heads, batch);

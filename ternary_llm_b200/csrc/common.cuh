@@ -43,6 +43,8 @@ int weight_unpack(const uint8_t* packed, int rows, int cols, uint32_t* nz, uint3
 int weight_register(const void* nz, const uint8_t* packed, int rows, int cols);
 int weight_unregister(const void* nz);
 int device_error_check(cudaStream_t stream);
+// Device error flag of the current device (nullptr if the library scratch cannot be set up).
+int* device_error_flag();
 int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, int rows, int cols, int rank,
                                  int world, void* const* peer_recv, void* epoch_local, int rows_max,
                                  cudaStream_t stream);

@@ -4,9 +4,9 @@
 // FP16 activations through the tensor-core GEMM for several tokens, INT8-quantised
 // activations through the streaming GEMV for one token -- but a single-token step makes
 // 10 launches per layer instead of 20 and never touches the host:
-//   RMSNorm with the previous residual add and the quantiser fused in | q,k,v in one GEMV |
+//   RMSNorm with the previous residual add and the quantiser fused in | q,k,v as one matrix |
 //   RoPE + cache append | attention (all query heads of a KV head per CTA, split over the
-//   cache) | quantise | o GEMV | add + RMSNorm + quantise | gate,up in one GEMV |
+//   cache) | quantise | o GEMV | add + RMSNorm + quantise | gate,up as one matrix |
 //   SwiGLU + quantise | down GEMV
 // The activation scale stays in device memory (the reference copies it to the host before
 // every GEMV, src/transformer.cpp:132-136), the position and the token live in device
@@ -28,6 +28,9 @@ struct PackedW {
 
 struct LayerW {
     PackedW q, k, v, o, gate, up, down;
+    // q,k,v and gate,up are packed back to back (their row counts are multiples of 16), so
+    // that a single-token step streams each group as ONE matrix: [q|k|v] and [gate|up].
+    PackedW qkv, gate_up;
     const half* attn_norm = nullptr;
     const half* ffn_norm = nullptr;
 };
@@ -41,6 +44,7 @@ struct Decoder {
     half *residual = nullptr, *hidden = nullptr, *hidden2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr;
     half *attn_out = nullptr, *gate = nullptr, *up = nullptr, *ffn_out = nullptr, *logits = nullptr;
     half *k_cache = nullptr, *v_cache = nullptr;
+    half *qkv1 = nullptr, *gu1 = nullptr;      // single-token outputs of the concatenated matrices
     int8_t* xq = nullptr;
     float* xscale = nullptr;
     float* attn_ws = nullptr;
@@ -72,16 +76,59 @@ int dev_alloc(Decoder* D, T** out, size_t n, bool zero)
     return TLLM_OK;
 }
 
-int pack(Decoder* D, const tllm_b200_ternary_weight& w, PackedW* out, cudaStream_t stream)
+int check_weight(const tllm_b200_ternary_weight& w)
 {
     if (!w.nonzero_masks || !w.sign_masks || !w.scales) return fail(TLLM_ERR_NULL, "decoder: null ternary weight");
-    if (w.in_features % kGroup) return fail(TLLM_ERR_SHAPE, "decoder: in_features=%d is not a multiple of 128", w.in_features);
+    if (w.out_features < 1 || w.in_features < kGroup || w.in_features % kGroup)
+        return fail(TLLM_ERR_SHAPE, "decoder: weight %d x %d: in_features must be a positive multiple of 128", w.out_features,
+                    w.in_features);
+    return TLLM_OK;
+}
+
+// dst == nullptr: allocate; else repack into dst (part of a concatenated buffer)
+int pack(Decoder* D, const tllm_b200_ternary_weight& w, PackedW* out, cudaStream_t stream, uint8_t* dst = nullptr)
+{
+    int st = check_weight(w);
+    if (st) return st;
     out->rows = w.out_features;
     out->cols = w.in_features;
-    int st = dev_alloc(D, &out->p, packed_bytes(w.out_features, w.in_features), false);
-    if (st) return st;
+    if (dst) out->p = dst;
+    else if ((st = dev_alloc(D, &out->p, packed_bytes(w.out_features, w.in_features), false))) return st;
     return weight_prepare(static_cast<const uint32_t*>(w.nonzero_masks), static_cast<const uint32_t*>(w.sign_masks),
                           static_cast<const half*>(w.scales), w.out_features, w.in_features, out->p, stream);
+}
+
+// Packs `count` matrices with the same input width back to back; `all` views them as one.
+int pack_group(Decoder* D, int count, const tllm_b200_ternary_weight* const* w, PackedW* const* out, PackedW* all,
+               cudaStream_t stream)
+{
+    int st;
+    size_t total = 0;
+    int rows = 0;
+    bool concat = true;
+    for (int i = 0; i < count; i++) {
+        if ((st = check_weight(*w[i]))) return st;
+        concat = concat && (w[i]->out_features % 16 == 0) && (w[i]->in_features == w[0]->in_features);
+        total += packed_bytes(w[i]->out_features, w[i]->in_features);
+        rows += w[i]->out_features;
+    }
+    if (!concat) {
+        *all = PackedW();
+        for (int i = 0; i < count; i++)
+            if ((st = pack(D, *w[i], out[i], stream))) return st;
+        return TLLM_OK;
+    }
+    uint8_t* base = nullptr;
+    if ((st = dev_alloc(D, &base, total, false))) return st;
+    size_t off = 0;
+    for (int i = 0; i < count; i++) {
+        if ((st = pack(D, *w[i], out[i], stream, base + off))) return st;
+        off += packed_bytes(w[i]->out_features, w[i]->in_features);
+    }
+    all->p = base;
+    all->rows = rows;
+    all->cols = w[0]->in_features;
+    return TLLM_OK;
 }
 
 // y[n_tokens, rows] = x[n_tokens, cols] . W^T with FP16 activations: the tcgen05 GEMM for
@@ -134,18 +181,26 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
         else
             TRY(launch_rmsnorm(D->ffn_out, L.attn_norm, D->hidden, D->residual, D->residual, xq, xs, n, hidden,
                                c.rms_norm_eps, 1, s));
-        {
+        half *qb = D->q, *kb = D->k, *vb = D->v, *gb = D->gate, *ub = D->up;
+        if (n == 1 && L.qkv.p) {
+            qb = D->qkv1;
+            kb = qb + qdim;
+            vb = kb + (size_t)c.n_kv_heads * c.head_dim;
+            const PackedW* w[1] = {&L.qkv};
+            half* y[1] = {qb};
+            TRY(linear_multi(D, 1, w, y, D->hidden, i8, n, s));
+        } else {
             const PackedW* w[3] = {&L.q, &L.k, &L.v};
-            half* y[3] = {D->q, D->k, D->v};
+            half* y[3] = {qb, kb, vb};
             TRY(linear_multi(D, 3, w, y, D->hidden, i8, n, s));
         }
-        TRY(launch_rope(D->q, D->k, D->v, D->k_cache + kv_off, D->v_cache + kv_off, 1, n, c.n_heads, c.n_kv_heads,
+        TRY(launch_rope(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, 1, n, c.n_heads, c.n_kv_heads,
                         c.head_dim, start_pos, pos_dev, c.rope_theta, c.max_seq_len, 1, s));
         if (pos_dev)
-            TRY(launch_attention(D->q, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
+            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
                                  c.head_dim, 1, 1, c.max_seq_len, pos_dev, D->attn_ws, D->attn_counters, s));
         else
-            TRY(launch_attention(D->q, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
+            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
                                  c.head_dim, n, start_pos + n, c.max_seq_len, nullptr, D->attn_ws, D->attn_counters, s));
         if (i8) TRY(launch_quantize_absmax_int8(D->attn_out, D->xq, D->xscale, qdim, s));
         {
@@ -155,16 +210,22 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
         }
         TRY(launch_rmsnorm(D->hidden2, L.ffn_norm, D->hidden, D->residual, D->residual, xq, xs, n, hidden, c.rms_norm_eps,
                            1, s));
-        {
+        if (n == 1 && L.gate_up.p) {
+            gb = D->gu1;
+            ub = gb + inter;
+            const PackedW* w[1] = {&L.gate_up};
+            half* y[1] = {gb};
+            TRY(linear_multi(D, 1, w, y, D->hidden, i8, n, s));
+        } else {
             const PackedW* w[2] = {&L.gate, &L.up};
-            half* y[2] = {D->gate, D->up};
+            half* y[2] = {gb, ub};
             TRY(linear_multi(D, 2, w, y, D->hidden, i8, n, s));
         }
-        TRY(launch_silu_mul(D->gate, D->up, D->gate, (long long)n * inter, xq, xs, s));
+        TRY(launch_silu_mul(gb, ub, gb, (long long)n * inter, xq, xs, s));
         {
             const PackedW* w[1] = {&L.down};
             half* y[1] = {D->ffn_out};
-            TRY(linear_multi(D, 1, w, y, D->gate, i8, n, s));
+            TRY(linear_multi(D, 1, w, y, gb, i8, n, s));
         }
     }
     // last residual add + final norm, last token only
@@ -230,10 +291,17 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
         if (!w.attn_norm_weight || !w.ffn_norm_weight) return bail(fail(TLLM_ERR_NULL, "decoder_create: null norm weight"));
         L.attn_norm = static_cast<const half*>(w.attn_norm_weight);
         L.ffn_norm = static_cast<const half*>(w.ffn_norm_weight);
-        const tllm_b200_ternary_weight* src[7] = {&w.q_proj, &w.k_proj, &w.v_proj, &w.o_proj, &w.gate_proj, &w.up_proj, &w.down_proj};
-        PackedW* dst[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
-        for (int i = 0; i < 7; i++)
-            if ((st = pack(D, *src[i], dst[i], D->stream))) return bail(st);
+        {
+            const tllm_b200_ternary_weight* src[3] = {&w.q_proj, &w.k_proj, &w.v_proj};
+            PackedW* dst[3] = {&L.q, &L.k, &L.v};
+            if ((st = pack_group(D, 3, src, dst, &L.qkv, D->stream))) return bail(st);
+        }
+        {
+            const tllm_b200_ternary_weight* src[2] = {&w.gate_proj, &w.up_proj};
+            PackedW* dst[2] = {&L.gate, &L.up};
+            if ((st = pack_group(D, 2, src, dst, &L.gate_up, D->stream))) return bail(st);
+        }
+        if ((st = pack(D, w.o_proj, &L.o, D->stream)) || (st = pack(D, w.down_proj, &L.down, D->stream))) return bail(st);
     }
     D->d.layers = nullptr;      // the caller's array is not referenced after this call
     if (!c.lm_head_weight && (st = pack(D, c.lm_head_ternary, &D->lm_head, D->stream))) return bail(st);
@@ -257,6 +325,8 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     ALLOC(dev_alloc(D, &D->logits, (size_t)c.vocab_size, true));
     ALLOC(dev_alloc(D, &D->k_cache, kv_elems, true));
     ALLOC(dev_alloc(D, &D->v_cache, kv_elems, true));
+    ALLOC(dev_alloc(D, &D->qkv1, qdim + 2 * kvdim, true));
+    ALLOC(dev_alloc(D, &D->gu1, (size_t)2 * c.intermediate_dim, true));
     ALLOC(dev_alloc(D, &D->xq, maxdim, true));
     ALLOC(dev_alloc(D, &D->xscale, 4, true));
     ALLOC(dev_alloc(D, &D->attn_ws, attention_workspace_bytes(1, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));

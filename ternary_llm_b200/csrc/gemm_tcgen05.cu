@@ -365,7 +365,6 @@ static EncodeTiledFn encode_fn()
 
 }  // namespace gemm
 
-int* device_error_flag();   // gemv_mma.cu
 
 bool gemm_tcgen05_supported(int M, int N, int K)
 {

@@ -59,8 +59,18 @@ __device__ __forceinline__ void quantize_staged(const float* vals, int n, int8_t
     const float absmax = block_max(m, sh);
     if (threadIdx.x == 0) *scale_out = (absmax > 0.f) ? (absmax / 127.0f) : 1.0f;
     const float inv = (absmax > 0.f) ? (127.0f / absmax) : 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x)
-        q[i] = (int8_t)max(-127, min(127, __float2int_rn(vals[i] * inv)));
+    if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(vals + 4 * i);
+            const int q0 = max(-127, min(127, __float2int_rn(v.x * inv))), q1 = max(-127, min(127, __float2int_rn(v.y * inv)));
+            const int q2 = max(-127, min(127, __float2int_rn(v.z * inv))), q3 = max(-127, min(127, __float2int_rn(v.w * inv)));
+            reinterpret_cast<uint32_t*>(q)[i] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
+                                                ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            q[i] = (int8_t)max(-127, min(127, __float2int_rn(vals[i] * inv)));
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -85,29 +95,72 @@ rmsnorm_kernel(const half* __restrict__ input, const half* __restrict__ weight, 
     const size_t base = (size_t)blockIdx.x * dim;
     pdl_wait();
 
-    float ss = 0.f;
-    for (int i = tid; i < dim; i += kNormThreads) {
-        float v = __half2float(input[base + i]);
-        if (residual) {
-            v += __half2float(residual[base + i]);
+    const half* xin = input + base;
+    const half* rin = residual ? residual + base : nullptr;
+    half* rout = residual_out ? residual_out + base : nullptr;
+    half* yout = output + base;
+    const bool vec = ((dim & 7) == 0) && (((reinterpret_cast<uintptr_t>(xin) | reinterpret_cast<uintptr_t>(rin) |
+                                            reinterpret_cast<uintptr_t>(rout) | reinterpret_cast<uintptr_t>(yout) |
+                                            reinterpret_cast<uintptr_t>(weight)) & 15) == 0);
+    // element-wise part of the first pass; returns the value kept for the second pass
+    auto first = [&](float x, float r, bool has_r, half& stored, float& ss) -> float {
+        float v = x;
+        if (has_r) {
+            v += r;
             if (!round_first) ss += v * v;
-            if (residual_out) {
-                const half r = __float2half_rn(v);
-                residual_out[base + i] = r;
-                v = __half2float(r);
+            if (rout) {
+                stored = __float2half_rn(v);
+                v = __half2float(stored);
             }
             if (round_first) ss += v * v;
         } else {
             ss += v * v;
         }
-        vals[i] = v;
+        return v;
+    };
+    float ss = 0.f;
+    if (vec) {
+        for (int i = tid; i < dim / 8; i += kNormThreads) {
+            const uint4 xr = *(reinterpret_cast<const uint4*>(xin) + i);
+            uint4 rr = make_uint4(0, 0, 0, 0);
+            if (rin) rr = *(reinterpret_cast<const uint4*>(rin) + i);
+            const half* xh = reinterpret_cast<const half*>(&xr);
+            const half* rh = reinterpret_cast<const half*>(&rr);
+            uint4 st4;
+            half* sth = reinterpret_cast<half*>(&st4);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                vals[i * 8 + j] = first(__half2float(xh[j]), __half2float(rh[j]), rin != nullptr, sth[j], ss);
+            if (rin && rout) *(reinterpret_cast<uint4*>(rout) + i) = st4;
+        }
+    } else {
+        for (int i = tid; i < dim; i += kNormThreads) {
+            half stored;
+            vals[i] = first(__half2float(xin[i]), rin ? __half2float(rin[i]) : 0.f, rin != nullptr, stored, ss);
+            if (rin && rout) rout[i] = stored;
+        }
     }
     const float var = block_sum(ss, sh) / (float)dim;
     const float rinv = rsqrtf(var + eps);
-    for (int i = tid; i < dim; i += kNormThreads) {
-        const half o = __float2half_rn(vals[i] * rinv * __half2float(weight[i]));
-        output[base + i] = o;
-        vals[i] = __half2float(o);
+    if (vec) {
+        for (int i = tid; i < dim / 8; i += kNormThreads) {
+            const uint4 wr = __ldg(reinterpret_cast<const uint4*>(weight) + i);
+            const half* wh = reinterpret_cast<const half*>(&wr);
+            uint4 st4;
+            half* sth = reinterpret_cast<half*>(&st4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                sth[j] = __float2half_rn(vals[i * 8 + j] * rinv * __half2float(wh[j]));
+                vals[i * 8 + j] = __half2float(sth[j]);
+            }
+            *(reinterpret_cast<uint4*>(yout) + i) = st4;
+        }
+    } else {
+        for (int i = tid; i < dim; i += kNormThreads) {
+            const half o = __float2half_rn(vals[i] * rinv * __half2float(weight[i]));
+            yout[i] = o;
+            vals[i] = __half2float(o);
+        }
     }
     if (q) {
         __syncthreads();
@@ -229,10 +282,28 @@ silu_mul_quant_kernel(const half* gate, const half* up, half* out, int8_t* __res
     __shared__ float sh[32];
     pdl_launch_dependents();
     pdl_wait();
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const half o = __float2half_rn(silu_mul(__half2float(gate[i]), __half2float(up[i])));
-        out[i] = o;
-        vals[i] = __half2float(o);
+    if ((size & 7) == 0 && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                             reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (int i = threadIdx.x; i < size / 8; i += blockDim.x) {
+            const uint4 gr = *(reinterpret_cast<const uint4*>(gate) + i);
+            const uint4 ur = *(reinterpret_cast<const uint4*>(up) + i);
+            const half* gh = reinterpret_cast<const half*>(&gr);
+            const half* uh = reinterpret_cast<const half*>(&ur);
+            uint4 st4;
+            half* sth = reinterpret_cast<half*>(&st4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                sth[j] = __float2half_rn(silu_mul(__half2float(gh[j]), __half2float(uh[j])));
+                vals[i * 8 + j] = __half2float(sth[j]);
+            }
+            *(reinterpret_cast<uint4*>(out) + i) = st4;
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const half o = __float2half_rn(silu_mul(__half2float(gate[i]), __half2float(up[i])));
+            out[i] = o;
+            vals[i] = __half2float(o);
+        }
     }
     __syncthreads();
     quantize_staged(vals, size, q, q_scale, sh);
