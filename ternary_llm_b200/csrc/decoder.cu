@@ -3,15 +3,16 @@
 // forward() keeps the reference's order of operations and its choice of arithmetic --
 // FP16 activations through the tensor-core GEMM for several tokens, INT8-quantised
 // activations through the streaming GEMV for one token -- but a single-token step makes
-// 10 launches per layer instead of 20 and never touches the host:
-//   RMSNorm with the previous residual add and the quantiser fused in | q,k,v as one matrix |
+// 7 launches per layer instead of 20 and never touches the host:
+//   [q|k|v] GEMV whose staging phase does residual add + RMSNorm + quantise |
 //   RoPE + cache append | attention (all query heads of a KV head per CTA, split over the
-//   cache) | quantise | o GEMV | add + RMSNorm + quantise | gate,up as one matrix |
-//   SwiGLU + quantise | down GEMV
+//   cache) | quantise | o GEMV | [gate|up] GEMV with add + RMSNorm + quantise in its staging |
+//   down GEMV with SwiGLU + quantise in its staging
 // The activation scale stays in device memory (the reference copies it to the host before
 // every GEMV, src/transformer.cpp:132-136), the position and the token live in device
 // memory too, and greedy sampling runs on the device, so that one decode step can be
 // captured as a CUDA graph and replayed.
+#include <utility>
 #include <vector>
 
 #include "layer.cuh"
@@ -45,6 +46,8 @@ struct Decoder {
     half *attn_out = nullptr, *gate = nullptr, *up = nullptr, *ffn_out = nullptr, *logits = nullptr;
     half *k_cache = nullptr, *v_cache = nullptr;
     half *qkv1 = nullptr, *gu1 = nullptr;      // single-token outputs of the concatenated matrices
+    half* residual2 = nullptr;                 // second residual vector of the fused single-token step
+    bool fused_ok = false;                     // every layer has concatenated q|k|v and gate|up
     int8_t* xq = nullptr;
     float* xscale = nullptr;
     float* attn_ws = nullptr;
@@ -172,6 +175,43 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
     int st;
 #define TRY(x) do { if ((st = (x)) != TLLM_OK) return st; } while (0)
     TRY(launch_embedding(static_cast<const half*>(c.embedding_table), tokens, D->residual, n, hidden, s));
+    half* res_cur = D->residual;
+    if (i8 && D->fused_ok) {
+        // Single token, INT8 activations: norm + quantise and SwiGLU + quantise happen inside the
+        // GEMVs' staging phase (7 launches per layer).  The residual alternates between two
+        // vectors because every CTA of a GEMV reads the old one while CTA 0 writes the new one.
+        half* res_next = D->residual2;
+        const size_t kvdim = (size_t)c.n_kv_heads * c.head_dim;
+        for (int l = 0; l < c.n_layers; l++) {
+            const LayerW& L = D->layers[l];
+            const size_t kv_off = (size_t)l * c.max_seq_len * kvdim;
+            half *qb = D->qkv1, *kb = qb + qdim, *vb = kb + kvdim, *gb = D->gu1, *ub = gb + inter;
+            if (l == 0) {
+                TRY(launch_gemv_int8_packed_norm(L.qkv.p, res_cur, nullptr, L.attn_norm, nullptr, c.rms_norm_eps, qb,
+                                                 L.qkv.rows, L.qkv.cols, s));
+            } else {
+                TRY(launch_gemv_int8_packed_norm(L.qkv.p, D->ffn_out, res_cur, L.attn_norm, res_next, c.rms_norm_eps, qb,
+                                                 L.qkv.rows, L.qkv.cols, s));
+                std::swap(res_cur, res_next);
+            }
+            TRY(launch_rope(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, 1, 1, c.n_heads, c.n_kv_heads, c.head_dim,
+                            start_pos, pos_dev, c.rope_theta, c.max_seq_len, 1, s));
+            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
+                                 c.head_dim, 1, pos_dev ? 1 : start_pos + 1, c.max_seq_len, pos_dev, D->attn_ws,
+                                 D->attn_counters, s));
+            TRY(launch_quantize_absmax_int8(D->attn_out, D->xq, D->xscale, qdim, s));
+            {
+                const uint8_t* p[1] = {L.o.p};
+                half* y[1] = {D->hidden2};
+                int rows[1] = {L.o.rows};
+                TRY(launch_gemv_int8_packed_multi(1, p, y, rows, L.o.cols, D->xq, D->xscale, s));
+            }
+            TRY(launch_gemv_int8_packed_norm(L.gate_up.p, D->hidden2, res_cur, L.ffn_norm, res_next, c.rms_norm_eps, gb,
+                                             L.gate_up.rows, L.gate_up.cols, s));
+            std::swap(res_cur, res_next);
+            TRY(launch_gemv_int8_packed_silu(L.down.p, gb, ub, D->ffn_out, L.down.rows, L.down.cols, s));
+        }
+    } else
     for (int l = 0; l < c.n_layers; l++) {
         const LayerW& L = D->layers[l];
         const size_t kv_off = (size_t)l * c.max_seq_len * c.n_kv_heads * c.head_dim;
@@ -232,8 +272,8 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
     const size_t last = (size_t)(n - 1) * hidden;
     const bool tern_head = (c.lm_head_weight == nullptr);
     const bool head_i8 = tern_head;     // a ternary lm_head always takes the INT8 path (src/transformer.cpp:308-311)
-    TRY(launch_rmsnorm(D->ffn_out + last, static_cast<const half*>(c.final_norm_weight), D->hidden, D->residual + last,
-                       D->residual + last, head_i8 ? D->xq : nullptr, head_i8 ? D->xscale : nullptr, 1, hidden,
+    TRY(launch_rmsnorm(D->ffn_out + last, static_cast<const half*>(c.final_norm_weight), D->hidden, res_cur + last,
+                       res_cur + last, head_i8 ? D->xq : nullptr, head_i8 ? D->xscale : nullptr, 1, hidden,
                        c.rms_norm_eps, 1, s));
     if (tern_head) {
         const uint8_t* p[1] = {D->lm_head.p};
@@ -303,6 +343,8 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
         }
         if ((st = pack(D, w.o_proj, &L.o, D->stream)) || (st = pack(D, w.down_proj, &L.down, D->stream))) return bail(st);
     }
+    D->fused_ok = true;
+    for (const LayerW& L : D->layers) D->fused_ok = D->fused_ok && L.qkv.p && L.gate_up.p;
     D->d.layers = nullptr;      // the caller's array is not referenced after this call
     if (!c.lm_head_weight && (st = pack(D, c.lm_head_ternary, &D->lm_head, D->stream))) return bail(st);
 
@@ -325,6 +367,7 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     ALLOC(dev_alloc(D, &D->logits, (size_t)c.vocab_size, true));
     ALLOC(dev_alloc(D, &D->k_cache, kv_elems, true));
     ALLOC(dev_alloc(D, &D->v_cache, kv_elems, true));
+    ALLOC(dev_alloc(D, &D->residual2, (size_t)c.hidden_dim, true));
     ALLOC(dev_alloc(D, &D->qkv1, qdim + 2 * kvdim, true));
     ALLOC(dev_alloc(D, &D->gu1, (size_t)2 * c.intermediate_dim, true));
     ALLOC(dev_alloc(D, &D->xq, maxdim, true));

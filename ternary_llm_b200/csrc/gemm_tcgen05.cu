@@ -390,6 +390,7 @@ static int launch_tm(gemm::EncodeTiledFn enc, const half* A, const gemm::Args& a
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr[dev]) {
         cudaFuncSetAttribute(gemm_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<TM>::kSmem);
+        cudaFuncSetAttribute(gemm_kernel<TM>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr[dev] = true;
     }
     const dim3 grid((a.N + kTileN - 1) / kTileN, (a.M + TM - 1) / TM);

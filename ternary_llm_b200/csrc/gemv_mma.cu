@@ -55,7 +55,9 @@ constexpr int kTickets = 64;                          // independent scratch reg
 constexpr int kMaxCtas = 256;
 constexpr int kMaxPeers = TLLM_MAX_PEERS;
 
-enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2 };
+// kI8Norm / kI8Silu: INT8 arithmetic like kI8, but the activation vector is produced inside
+// the kernel's staging phase from FP16 inputs (fused_x.cuh semantics below).
+enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4 };
 
 struct GemvArgs {
     const uint8_t* packed;
@@ -63,6 +65,15 @@ struct GemvArgs {
     half* y;                // half [batch, rows]
     float in_scale;         // INT8 mode: activation scale
     const float* in_scale_dev;  // INT8 mode: when not null the scale is read from device memory instead
+    // kI8Norm: x = quantise(rmsnorm(fx_a (+ fx_b)) * fx_w); the FP16-rounded sum fx_a + fx_b is
+    //          written to fx_res_out by CTA 0 when both are given.
+    // kI8Silu: x = quantise(silu(fx_a) * fx_b).
+    const half* fx_a;
+    const half* fx_b;
+    const half* fx_w;
+    half* fx_res_out;
+    float fx_eps;
+    int off_xtmp;           // shared memory: half [cols] staging + 64 floats of reduction scratch
     int rows, cols, groups; // groups = cols / 128 = tiles per row block
     int batch;              // 1 or 2 vectors handled by this launch
     int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
@@ -245,6 +256,115 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
     }
 }
 
+// Block-wide reductions over the CTA's kWarps warps; `red` is 33 floats of shared memory.
+__device__ __forceinline__ float cta_sum(float v, float* red, int tid)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    if (tid < 32) {
+        float t = (tid < kWarps) ? red[tid] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (tid == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float cta_max(float v, float* red, int tid)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    if (tid < 32) {
+        float t = (tid < kWarps) ? red[tid] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+        if (tid == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// The activation vector of an INT8 GEMV produced in place by every CTA from FP16 inputs,
+// instead of by a single-CTA kernel in front of the GEMV (a few microseconds of launch
+// and dependency latency per operator in a decode step).  Each CTA reads the inputs
+// (they sit in L2), so the work is replicated, not the traffic to HBM.
+//   kI8Norm  the engine's "residual add, RMSNorm, absmax quantise" (reference
+//            src/transformer.cpp:252-268 with kernels/rmsnorm.cu and kernels/activations.cu:88-142):
+//            v = half(a + b) (or a when b is null), var = mean(v^2), o = half(v * rsqrt(var + eps) * w),
+//            scale = absmax(o) / 127 (1 if zero), q = clamp(rint(o * 127 / absmax)).
+//   kI8Silu  "SwiGLU, absmax quantise" (src/transformer.cpp:284-288): o = half(silu(a) * b), then as above.
+// Returns the activation scale.  tmp: half [cols]; red: 33 floats.
+template <int MODE>
+__device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, half* tmp, float* red, int tid)
+{
+    const int n8 = a.cols >> 3;
+    float ss = 0.f, mx = 0.f;
+    for (int i = tid; i < n8; i += kThreads) {
+        const uint4 ar = *(reinterpret_cast<const uint4*>(a.fx_a) + i);
+        uint4 br = make_uint4(0, 0, 0, 0);
+        if (a.fx_b) br = *(reinterpret_cast<const uint4*>(a.fx_b) + i);
+        const half* ah = reinterpret_cast<const half*>(&ar);
+        const half* bh = reinterpret_cast<const half*>(&br);
+        uint4 st4;
+        half* sth = reinterpret_cast<half*>(&st4);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (MODE == kI8Silu) {
+                const float g = __half2float(ah[j]);
+                sth[j] = __float2half_rn(g / (1.0f + expf(-g)) * __half2float(bh[j]));
+                mx = fmaxf(mx, fabsf(__half2float(sth[j])));
+            } else {
+                sth[j] = a.fx_b ? __float2half_rn(__half2float(ah[j]) + __half2float(bh[j])) : ah[j];
+                const float v = __half2float(sth[j]);
+                ss += v * v;
+            }
+        }
+        *(reinterpret_cast<uint4*>(tmp) + i) = st4;
+        if (MODE == kI8Norm && a.fx_res_out && a.fx_b && blockIdx.x == 0) *(reinterpret_cast<uint4*>(a.fx_res_out) + i) = st4;
+    }
+    if (MODE == kI8Norm) {
+        const float var = cta_sum(ss, red, tid) / (float)a.cols;
+        const float rinv = rsqrtf(var + a.fx_eps);
+        for (int i = tid; i < n8; i += kThreads) {
+            uint4 v4 = *(reinterpret_cast<const uint4*>(tmp) + i);
+            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(a.fx_w) + i);
+            half* vh = reinterpret_cast<half*>(&v4);
+            const half* wh = reinterpret_cast<const half*>(&w4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                vh[j] = __float2half_rn(__half2float(vh[j]) * rinv * __half2float(wh[j]));
+                mx = fmaxf(mx, fabsf(__half2float(vh[j])));
+            }
+            *(reinterpret_cast<uint4*>(tmp) + i) = v4;
+        }
+    }
+    const float absmax = cta_max(mx, red, tid);
+    const float inv = (absmax > 0.f) ? (127.0f / absmax) : 0.f;
+    for (int i = tid; i < n8; i += kThreads) {
+        const uint4 v4 = *(reinterpret_cast<const uint4*>(tmp) + i);
+        const half* vh = reinterpret_cast<const half*>(&v4);
+        uint32_t w[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int qv = max(-127, min(127, __float2int_rn(__half2float(vh[h * 4 + j]) * inv)));
+                acc |= (uint32_t)(qv & 0xff) << (8 * j);
+            }
+            w[h] = acc;
+        }
+        *(reinterpret_cast<uint2*>(xq) + i) = make_uint2(w[0], w[1]);
+    }
+    return (absmax > 0.f) ? (absmax / 127.0f) : 1.0f;
+}
+
 // One tile (one scale group of a 16-row block): four k32 MMA steps.  Returns the
 // weighted integer group sums of rows gq (p0) and gq+8 (p1).
 //   xq4: FP16 modes, this lane's 128-bit B words of the group (step pairs at [0], [LANES])
@@ -289,7 +409,8 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const GemvArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr bool I8 = (MODE == kI8);
+    constexpr bool I8 = (MODE == kI8 || MODE == kI8Norm || MODE == kI8Silu);
+    constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu);
     constexpr int LANES = (MODE == kF16B2) ? 32 : 16;
 
     asm volatile("griddepcontrol.launch_dependents;");
@@ -341,7 +462,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     asm volatile("griddepcontrol.wait;" ::: "memory");
     PHASE(2);
 
-    if (I8) {
+    float fused_scale = 1.0f;
+    if (FUSEDX) {
+        fused_scale = stage_x_fused<MODE>(a, reinterpret_cast<int8_t*>(xstage), reinterpret_cast<half*>(smem + a.off_xtmp),
+                                          reinterpret_cast<float*>(smem + a.off_xtmp + (size_t)a.cols * sizeof(half)), tid);
+    } else if (I8) {
         const int n16 = a.cols / 16;
         const uint4* src = reinterpret_cast<const uint4*>(a.x);
         for (int i = tid; i < n16; i += kThreads) reinterpret_cast<uint4*>(xstage)[i] = __ldg(src + i);
@@ -456,7 +581,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
 
     // ---- reduction: warps of this CTA, then CTAs, row block by row block -----------
     const int nb = (MODE == kF16B2) ? a.batch : 1;
-    const float oscale = I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f;
+    const float oscale = FUSEDX ? fused_scale : (I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f);
     float* myrec = a.ws + (size_t)blockIdx.x * 64;
 
     if (a.ar_world > 0) {
@@ -940,6 +1065,7 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     cudaGetDevice(&dev);
     if (!attr[dev]) {
         cudaFuncSetAttribute(gemv_packed_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(gemv_packed_kernel<MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -962,8 +1088,17 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
 }
 
 // x: half [batch, cols] (mode f16) or int8 [cols]; batch 1..2 per launch.
+struct FusedX {
+    const half* a;
+    const half* b;
+    const half* w;
+    half* res_out;
+    float eps;
+};
+
 static int launch_packed_once(const uint8_t* packed, const void* x, half* y, float in_scale, int mode,
-                              int batch, int rows, int cols, cudaStream_t stream, const float* in_scale_dev = nullptr)
+                              int batch, int rows, int cols, cudaStream_t stream, const float* in_scale_dev = nullptr,
+                              const FusedX* fx = nullptr)
 {
     DeviceScratch* s = nullptr;
     int st = get_scratch(&s);
@@ -974,6 +1109,13 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.y = y;
     a.in_scale = in_scale;
     a.in_scale_dev = in_scale_dev;
+    if (fx) {
+        a.fx_a = fx->a;
+        a.fx_b = fx->b;
+        a.fx_w = fx->w;
+        a.fx_res_out = fx->res_out;
+        a.fx_eps = fx->eps;
+    }
     a.rows = rows;
     a.cols = cols;
     a.groups = cols / kGroup;
@@ -993,6 +1135,9 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     // matrix is a few hundred KB, latency-bound, and the cross-CTA combine would cost more
     // than the idle SMs; one CTA per row block.
     if (nrb < grid && a.groups <= kWarps * kSlotTiles) a.aligned = 1;
+    // The same holds with a few more row blocks than SMs when a CTA's share is still at most
+    // one ring slot per warp (q|k|v of a small model: 192 row blocks of 16 tiles).
+    if (per_cta_rb * a.groups <= kWarps * kSlotTiles) a.aligned = 1;
     const int items = a.aligned ? nrb : tiles;
     if (items < grid) grid = items;
     a.part_q = items / grid;
@@ -1007,7 +1152,8 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.err = s->misc + 1;
     // shared memory: activations | xfac | partial sums | rings | mbarriers
     size_t xbytes;
-    if (mode == kI8) xbytes = (size_t)cols;
+    const bool fusedx = (mode == kI8Norm || mode == kI8Silu);
+    if (mode == kI8 || fusedx) xbytes = (size_t)cols;
     else xbytes = (size_t)a.groups * 2 * ((mode == kF16B2) ? 32 : 16) * 16;
     size_t off = (xbytes + 15) & ~(size_t)15;
     a.off_xfac = (int)off;
@@ -1021,11 +1167,18 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     off += (size_t)kWarps * kRing * kSlotBytes;
     a.off_bar = (int)off;
     off += (size_t)kWarps * kRing * 8;
+    if (fusedx) {
+        off = (off + 15) & ~(size_t)15;
+        a.off_xtmp = (int)off;
+        off += (size_t)cols * sizeof(half) + 64 * sizeof(float);
+    }
     if (off > 227 * 1024)
         return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d needs %zu bytes of shared memory (limit 232448)", rows, cols, off);
     switch (mode) {
         case kF16B1: return launch_mode<kF16B1>(a, grid, off, stream, s);
         case kF16B2: return launch_mode<kF16B2>(a, grid, off, stream, s);
+        case kI8Norm: return launch_mode<kI8Norm>(a, grid, off, stream, s);
+        case kI8Silu: return launch_mode<kI8Silu>(a, grid, off, stream, s);
         default: return launch_mode<kI8>(a, grid, off, stream, s);
     }
 }
@@ -1049,6 +1202,7 @@ static int launch_cw_t(const CwArgs& a, int grid, size_t smem, cudaStream_t stre
     cudaGetDevice(&dev);
     if (!attr[dev]) {
         cudaFuncSetAttribute(gemv_cw_kernel<MODE, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(gemv_cw_kernel<MODE, RING>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -1159,6 +1313,23 @@ int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half*
     return gemv_packed_multi_any(count, packed, y, rows, cols, nullptr, xq, scale_dev, stream);
 }
 
+// INT8 GEMV whose activation vector is made inside the kernel (stage_x_fused):
+// y = W . quantise(rmsnorm(a (+ b)) * w) with the rounded sum a + b stored to res_out, or
+// y = W . quantise(silu(a) * b) when w == nullptr.
+int launch_gemv_int8_packed_norm(const uint8_t* packed, const half* a, const half* b, const half* w, half* res_out,
+                                 float eps, half* y, int rows, int cols, cudaStream_t stream)
+{
+    const FusedX fx = {a, b, w, res_out, eps};
+    return launch_packed_once(packed, nullptr, y, 1.0f, kI8Norm, 1, rows, cols, stream, nullptr, &fx);
+}
+
+int launch_gemv_int8_packed_silu(const uint8_t* packed, const half* gate, const half* up, half* y, int rows, int cols,
+                                 cudaStream_t stream)
+{
+    const FusedX fx = {gate, up, nullptr, nullptr, 0.f};
+    return launch_packed_once(packed, nullptr, y, 1.0f, kI8Silu, 1, rows, cols, stream, nullptr, &fx);
+}
+
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
                        cudaStream_t stream)
 {
@@ -1245,6 +1416,9 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     // matrix is a few hundred KB, latency-bound, and the cross-CTA combine would cost more
     // than the idle SMs; one CTA per row block.
     if (nrb < grid && a.groups <= kWarps * kSlotTiles) a.aligned = 1;
+    // The same holds with a few more row blocks than SMs when a CTA's share is still at most
+    // one ring slot per warp (q|k|v of a small model: 192 row blocks of 16 tiles).
+    if (per_cta_rb * a.groups <= kWarps * kSlotTiles) a.aligned = 1;
     const int items = a.aligned ? nrb : tiles;
     if (items < grid) grid = items;
     a.part_q = items / grid;

@@ -9,6 +9,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <unordered_set>
+
 #include "common.cuh"
 
 namespace tllm {
@@ -16,10 +19,27 @@ namespace tllm {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Every kernel of the library asks for the largest shared-memory carve-out.  The streaming
+// GEMV needs it (two CTAs of about 90 KB per SM); if its neighbours in a decode step ran
+// with another split of the SM's L1/shared memory, each change of kernel would have to wait
+// for the SMs to drain and be reconfigured, which defeats the overlap of consecutive launches.
+inline void prefer_max_shared(const void* kernel)
+{
+    static std::mutex mu;
+    static std::unordered_set<unsigned long long> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned long long key = (unsigned long long)reinterpret_cast<uintptr_t>(kernel) * 64ull + (unsigned)dev;
+    std::lock_guard<std::mutex> lk(mu);
+    if (done.insert(key).second)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 template <typename... KArgs, typename... Args>
 int launch_pdl(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                Args... args)
 {
+    prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

@@ -104,6 +104,9 @@ int launch_quantize_absmax_int8(const half* x, int8_t* q, float* scale, int n, c
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaFuncSetAttribute(quantize_absmax_int8_kernel,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        // same carve-out as the GEMV that follows: no reconfiguration of the SMs between the two
+        cudaFuncSetAttribute(quantize_absmax_int8_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
         configured[dev] = true;
     }
     quantize_absmax_int8_kernel<<<1, kQuantThreads, smem, stream>>>(x, q, scale, n);
