@@ -286,6 +286,360 @@ attention_kernel(const AttnArgs a)
     }
 }
 
+// ---------------------------------------------------------------------------
+// Single-token step: rotary embedding, cache append and attention in one launch
+// ---------------------------------------------------------------------------
+// What the reference does with rope_forward, copy_to_kv_cache and attention_forward
+// (src/transformer.cpp:225-245) for one new token.  Grid (splits, KV heads); a CTA owns
+// 128 cache positions of one KV head and the query heads that share it.  After the
+// dependency wait the CTA immediately requests its slice of K and V (bulk copies of the
+// positions written by earlier steps), and while they fly it rotates the group's queries
+// into shared memory; the CTA whose slice holds the new position also rotates the new key,
+// puts key and value into its shared-memory slice and appends them to the cache.  Scores and
+// softmax as in attention_kernel; P.V runs with one thread per (head, channel pair) and
+// several position groups in parallel, reduced through shared memory.  Splits merge through
+// the last-arriver scheme of attention_kernel.
+constexpr int kDecChunk = 128;
+constexpr int kDecMaxItems = 8;       // (head, channel pair) items per thread
+
+struct DecodeArgs {
+    half* q;                   // [n_heads, hd] of the new token, rotated in shared memory only
+    const half* k;             // [n_kv_heads, hd] new key (unrotated)
+    const half* v;             // [n_kv_heads, hd] new value
+    half* k_cache;
+    half* v_cache;
+    half* out;                 // [n_heads, hd]
+    int n_heads, n_kv_heads, head_dim, kv_len_max;
+    int pos;                   // position of the new token (pos_dev overrides)
+    const int* pos_dev;
+    float theta;
+    int nsplit;
+    float* ws;
+    unsigned* counters;
+    int* err;
+};
+
+__global__ void __launch_bounds__(kAttnThreads)
+attention_decode_kernel(const DecodeArgs a)
+{
+    extern __shared__ __align__(16) float smem[];
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, hp = hd >> 1;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int split = blockIdx.x, kvh = blockIdx.y;
+
+    half* ks = reinterpret_cast<half*>(smem);                     // [kDecChunk][hd]
+    half* vs = ks + kDecChunk * hd;                               // [kDecChunk][hd]
+    float* qs = reinterpret_cast<float*>(vs + kDecChunk * hd);    // [G][hd]
+    float* ps = qs + G * hd;                                      // [G][kDecChunk]
+    float* m_run = ps + G * kDecChunk;
+    float* l_run = m_run + kAttnMaxGroup;
+    float* corr = l_run + kAttnMaxGroup;
+    float* red = corr + kAttnMaxGroup;                            // P.V partials [groups][G*hd]
+    __shared__ int s_last;
+    __shared__ int s_ok;
+    __shared__ __align__(8) unsigned long long s_bar;
+    const uint32_t bar = smem_u32(&s_bar);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // rotation frequency of this thread's channel pairs (independent of the position)
+    const int npairs = G * hp;                                    // query pairs of the group
+    float freq[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const int pr = (tid + u * kAttnThreads) % hp;
+        freq[u] = 1.0f / powf(a.theta, (2.0f * (float)pr) / (float)hd);
+    }
+    __syncthreads();
+
+    pdl_wait();
+    const int pos = a.pos_dev ? *a.pos_dev : a.pos;
+    const int limit = pos + 1;
+    int nactive = (limit + kDecChunk - 1) / kDecChunk;
+    if (nactive > a.nsplit) nactive = a.nsplit;
+    if (split >= nactive) return;
+    const int lo = split * kDecChunk;
+    const int hi = (split == nactive - 1) ? limit : lo + kDecChunk;
+    const bool owns_new = (split == nactive - 1);                 // this CTA's range ends with the new position
+
+    const size_t cache_base = (size_t)kvh * (size_t)a.kv_len_max * hd;
+    half* kb = a.k_cache + cache_base;
+    half* vb = a.v_cache + cache_base;
+    const float scale = rsqrtf((float)hd);
+
+    const int items = G * hp;                                     // (head, channel pair) outputs
+    const int pgroups = (items < kAttnThreads) ? kAttnThreads / items : 1;
+    const int nitem = (items + kAttnThreads - 1) / kAttnThreads;  // items per thread when pgroups == 1
+    float2 o[kDecMaxItems];
+#pragma unroll
+    for (int e = 0; e < kDecMaxItems; e++) o[e] = make_float2(0.f, 0.f);
+    if (tid < G) {
+        m_run[tid] = -FLT_MAX;
+        l_run[tid] = 0.f;
+    }
+
+    uint32_t phase = 0;
+    for (int c0 = lo; c0 < hi; c0 += kDecChunk) {
+        const int nc = min(kDecChunk, hi - c0);
+        const bool has_new = owns_new && (c0 + nc == limit);
+        const int nold = has_new ? nc - 1 : nc;                   // positions that come from the cache
+        if (tid == 0 && nold > 0) {
+            const uint32_t bytes = (uint32_t)nold * hd * sizeof(half);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(ks)), "l"(kb + (size_t)c0 * hd), "r"(bytes), "r"(bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(vs)), "l"(vb + (size_t)c0 * hd), "r"(bytes), "r"(bar) : "memory");
+        }
+        if (c0 == lo) {
+            // queries: rotate, scale, keep in shared memory (the global q is left as it was)
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = tid + u * kAttnThreads;
+                if (i < npairs) {
+                    const int g = i / hp, pr = i - g * hp;
+                    const float2 x = __half22float2(*(reinterpret_cast<const half2*>(a.q + ((size_t)kvh * G + g) * hd) + pr));
+                    float sn, cs;
+                    sincosf((float)pos * freq[u], &sn, &cs);
+                    // rounded to FP16 like the rotated q the reference stores, then scaled
+                    qs[g * hd + 2 * pr] = __half2float(__float2half_rn(x.x * cs - x.y * sn)) * scale;
+                    qs[g * hd + 2 * pr + 1] = __half2float(__float2half_rn(x.x * sn + x.y * cs)) * scale;
+                }
+            }
+        }
+        if (has_new && tid < hp) {
+            // the new key (rotated) and value: into this slice and appended to the cache
+            const float2 x = __half22float2(*(reinterpret_cast<const half2*>(a.k + (size_t)kvh * hd) + tid));
+            float sn, cs;
+            sincosf((float)pos * (1.0f / powf(a.theta, (2.0f * (float)tid) / (float)hd)), &sn, &cs);
+            const half2 kr = __halves2half2(__float2half_rn(x.x * cs - x.y * sn), __float2half_rn(x.x * sn + x.y * cs));
+            const half2 vr = *(reinterpret_cast<const half2*>(a.v + (size_t)kvh * hd) + tid);
+            *(reinterpret_cast<half2*>(ks + (size_t)(nc - 1) * hd) + tid) = kr;
+            *(reinterpret_cast<half2*>(vs + (size_t)(nc - 1) * hd) + tid) = vr;
+            if (pos < a.kv_len_max) {
+                *(reinterpret_cast<half2*>(kb + (size_t)pos * hd) + tid) = kr;
+                *(reinterpret_cast<half2*>(vb + (size_t)pos * hd) + tid) = vr;
+            }
+        }
+        if (tid == 0) s_ok = (nold > 0) ? (mbar_wait_bounded(bar, phase) ? 1 : 0) : 1;
+        if (nold > 0) phase ^= 1u;
+        __syncthreads();
+        if (!s_ok) {
+            if (tid == 0 && a.err) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+            return;
+        }
+        // ---- scores: thread j <-> position c0 + j ----------------------------------
+        if (tid < nc) {
+            float dot[kAttnMaxGroup];
+#pragma unroll
+            for (int g = 0; g < kAttnMaxGroup; g++) dot[g] = 0.f;
+            const uint4* k4 = reinterpret_cast<const uint4*>(ks + (size_t)tid * hd);
+            const int nd8 = hd >> 3;
+            int d8 = tid % nd8;
+            for (int i8 = 0; i8 < nd8; i8++) {
+                const uint4 raw = k4[d8];
+                const half2* h = reinterpret_cast<const half2*>(&raw);
+                float kf[8];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    kf[2 * j] = f.x;
+                    kf[2 * j + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < kAttnMaxGroup; g++) {
+                    if (g < G) {
+                        const float4 q0 = *reinterpret_cast<const float4*>(qs + g * hd + d8 * 8);
+                        const float4 q1 = *reinterpret_cast<const float4*>(qs + g * hd + d8 * 8 + 4);
+                        dot[g] += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x +
+                                  kf[5] * q1.y + kf[6] * q1.z + kf[7] * q1.w;
+                    }
+                }
+                d8 = (d8 + 1 == nd8) ? 0 : d8 + 1;
+            }
+#pragma unroll
+            for (int g = 0; g < kAttnMaxGroup; g++)
+                if (g < G) ps[g * kDecChunk + tid] = dot[g];
+        }
+        __syncthreads();
+        for (int g = warp; g < G; g += kAttnThreads / 32) {
+            float* p = ps + g * kDecChunk;
+            float mx = -FLT_MAX;
+            for (int j = lane; j < nc; j += 32) mx = fmaxf(mx, p[j]);
+            mx = warp_max(mx);
+            const float m_old = m_run[g];
+            const float m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int j = lane; j < nc; j += 32) {
+                const float e = __expf(p[j] - m_new);
+                p[j] = e;
+                sum += e;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float c = __expf(m_old - m_new);
+                corr[g] = c;
+                l_run[g] = l_run[g] * c + sum;
+                m_run[g] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- P.V: thread <-> (head, channel pair) x position group ---------------------
+        if (pgroups > 1) {
+            const int item = tid % items, pg = tid / items;
+            if (pg < pgroups) {
+                const int g = item / hp, pr = item - g * hp;
+                const float* p = ps + g * kDecChunk;
+                const half2* vp = reinterpret_cast<const half2*>(vs) + pr;
+                float2 acc = make_float2(o[0].x * corr[g], o[0].y * corr[g]);
+                for (int j = pg; j < nc; j += pgroups) {
+                    const float2 vv = __half22float2(vp[(size_t)j * hp]);
+                    acc.x = fmaf(p[j], vv.x, acc.x);
+                    acc.y = fmaf(p[j], vv.y, acc.y);
+                }
+                o[0] = acc;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < kDecMaxItems; e++) {
+                const int item = e * kAttnThreads + tid;
+                if (e < nitem && item < items) {
+                    const int g = item / hp, pr = item - g * hp;
+                    const float* p = ps + g * kDecChunk;
+                    const half2* vp = reinterpret_cast<const half2*>(vs) + pr;
+                    float2 acc = make_float2(o[e].x * corr[g], o[e].y * corr[g]);
+                    for (int j = 0; j < nc; j++) {
+                        const float2 vv = __half22float2(vp[(size_t)j * hp]);
+                        acc.x = fmaf(p[j], vv.x, acc.x);
+                        acc.y = fmaf(p[j], vv.y, acc.y);
+                    }
+                    o[e] = acc;
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- reduce the position groups, then write or publish ------------------------------
+    if (pgroups > 1) {
+        const int item = tid % items, pg = tid / items;
+        if (pg < pgroups && pg > 0) *reinterpret_cast<float2*>(red + ((size_t)(pg - 1) * items + item) * 2) = o[0];
+        __syncthreads();
+        if (pg == 0)
+            for (int r = 0; r < pgroups - 1; r++) {
+                const float2 t = *reinterpret_cast<const float2*>(red + ((size_t)r * items + item) * 2);
+                o[0].x += t.x;
+                o[0].y += t.y;
+            }
+    }
+    const bool writer_all = (pgroups == 1);
+    half* op = a.out + (size_t)kvh * G * hd;
+    const int rec = G * (hd + 2);
+    float* my = a.ws + ((size_t)kvh * a.nsplit + split) * rec;
+#pragma unroll
+    for (int e = 0; e < kDecMaxItems; e++) {
+        const int item = writer_all ? e * kAttnThreads + tid : tid;
+        const bool mine = writer_all ? (e < nitem && item < items) : (e == 0 && tid < items);
+        if (mine) {
+            const int g = item / hp, pr = item - g * hp;
+            if (nactive == 1) {
+                const float l = l_run[g];
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                *(reinterpret_cast<half2*>(op + (size_t)g * hd) + pr) =
+                    __halves2half2(__float2half_rn(o[e].x * inv), __float2half_rn(o[e].y * inv));
+            } else {
+                *reinterpret_cast<float2*>(my + (size_t)g * hd + 2 * pr) = o[e];
+            }
+        }
+    }
+    if (nactive == 1) return;
+    if (tid < G) {
+        my[G * hd + tid] = m_run[tid];
+        my[G * hd + G + tid] = l_run[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* cnt = a.counters + kvh;
+        s_last = (atomicAdd(cnt, 1u) == (unsigned)(nactive - 1)) ? 1 : 0;
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* base = a.ws + (size_t)kvh * a.nsplit * rec;
+    for (int idx = tid; idx < G * hd; idx += kAttnThreads) {
+        const int g = idx / hd;
+        float m = -FLT_MAX;
+        for (int sidx = 0; sidx < nactive; sidx++) m = fmaxf(m, __ldcg(base + (size_t)sidx * rec + G * hd + g));
+        float num = 0.f, den = 0.f;
+        for (int sidx = 0; sidx < nactive; sidx++) {
+            const float w = __expf(__ldcg(base + (size_t)sidx * rec + G * hd + g) - m);
+            num = fmaf(w, __ldcg(base + (size_t)sidx * rec + idx), num);
+            den = fmaf(w, __ldcg(base + (size_t)sidx * rec + G * hd + G + g), den);
+        }
+        op[idx] = __float2half_rn(den > 0.f ? num / den : 0.f);
+    }
+}
+
+size_t attention_decode_workspace_bytes(int n_heads, int n_kv_heads, int head_dim, int kv_len_max)
+{
+    const int G = n_heads / n_kv_heads;
+    const int nsplit = (kv_len_max + kDecChunk - 1) / kDecChunk;
+    return (size_t)n_kv_heads * nsplit * G * (head_dim + 2) * sizeof(float);
+}
+
+// One new token at position pos (or *pos_dev): q [n_heads, hd], k and v [n_kv_heads, hd] as
+// the projections wrote them; the rotated key and the value are appended to the caches.
+// ws: attention_decode_workspace_bytes; counters: n_kv_heads zero-initialised unsigned.
+int launch_attention_decode(half* q, const half* k, const half* v, half* k_cache, half* v_cache, half* out, int n_heads,
+                            int n_kv_heads, int head_dim, int kv_len_max, int pos, const int* pos_dev, float theta,
+                            float* ws, unsigned* counters, cudaStream_t stream)
+{
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(TLLM_ERR_SHAPE, "attention: n_heads=%d n_kv_heads=%d", n_heads, n_kv_heads);
+    const int G = n_heads / n_kv_heads;
+    const int items = G * head_dim / 2;
+    if (G > kAttnMaxGroup || head_dim % 8 || head_dim > 128 || head_dim / 2 > kAttnThreads ||
+        items > kDecMaxItems * kAttnThreads || G * head_dim / 2 > 4 * kAttnThreads)
+        return fail(TLLM_ERR_SHAPE, "attention: head_dim=%d with %d heads per group is not supported", head_dim, G);
+    if (!pos_dev && (pos < 0 || pos >= kv_len_max)) return fail(TLLM_ERR_SHAPE, "attention: pos=%d kv_len_max=%d", pos, kv_len_max);
+    DecodeArgs a = {};
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.k_cache = k_cache;
+    a.v_cache = v_cache;
+    a.out = out;
+    a.n_heads = n_heads;
+    a.n_kv_heads = n_kv_heads;
+    a.head_dim = head_dim;
+    a.kv_len_max = kv_len_max;
+    a.pos = pos;
+    a.pos_dev = pos_dev;
+    a.theta = theta;
+    a.nsplit = (kv_len_max + kDecChunk - 1) / kDecChunk;
+    a.ws = ws;
+    a.counters = counters;
+    a.err = device_error_flag();
+    const int pgroups = (items < kAttnThreads) ? kAttnThreads / items : 1;
+    const size_t smem = (size_t)2 * kDecChunk * head_dim * sizeof(half) +
+                        ((size_t)G * head_dim + (size_t)G * kDecChunk + 3 * kAttnMaxGroup +
+                         (size_t)(pgroups > 1 ? (pgroups - 1) * items * 2 : 0)) * sizeof(float);
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr[dev]) {
+        cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr[dev] = true;
+    }
+    return launch_pdl("attention_decode", attention_decode_kernel, dim3(a.nsplit, n_kv_heads), dim3(kAttnThreads), smem,
+                      stream, a);
+}
+
 size_t attention_workspace_bytes(int batch, int n_heads, int n_kv_heads, int head_dim, int kv_len_max)
 {
     const int G = n_heads / n_kv_heads;

@@ -55,10 +55,12 @@ int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half*
 // INT8 GEMVs that build their activation vector inside the kernel from FP16 inputs:
 //   norm: x = quantise(rmsnorm(a (+ b)) * w), half(a + b) stored to res_out (may be null)
 //   silu: x = quantise(silu(gate) * up)
+//   quant: x = quantise(x_f16)
 int launch_gemv_int8_packed_norm(const uint8_t* packed, const half* a, const half* b, const half* w, half* res_out,
                                  float eps, half* y, int rows, int cols, cudaStream_t stream);
 int launch_gemv_int8_packed_silu(const uint8_t* packed, const half* gate, const half* up, half* y, int rows, int cols,
                                  cudaStream_t stream);
+int launch_gemv_int8_packed_quant(const uint8_t* packed, const half* x, half* y, int rows, int cols, cudaStream_t stream);
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream);
 

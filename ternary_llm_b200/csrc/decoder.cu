@@ -3,10 +3,11 @@
 // forward() keeps the reference's order of operations and its choice of arithmetic --
 // FP16 activations through the tensor-core GEMM for several tokens, INT8-quantised
 // activations through the streaming GEMV for one token -- but a single-token step makes
-// 7 launches per layer instead of 20 and never touches the host:
+// 5 launches per layer instead of 20 and never touches the host:
 //   [q|k|v] GEMV whose staging phase does residual add + RMSNorm + quantise |
-//   RoPE + cache append | attention (all query heads of a KV head per CTA, split over the
-//   cache) | quantise | o GEMV | [gate|up] GEMV with add + RMSNorm + quantise in its staging |
+//   RoPE + cache append + attention (all query heads of a KV head per CTA, split over the
+//   cache) | o GEMV with the quantiser in its staging |
+//   [gate|up] GEMV with add + RMSNorm + quantise in its staging |
 //   down GEMV with SwiGLU + quantise in its staging
 // The activation scale stays in device memory (the reference copies it to the host before
 // every GEMV, src/transformer.cpp:132-136), the position and the token live in device
@@ -51,6 +52,7 @@ struct Decoder {
     int8_t* xq = nullptr;
     float* xscale = nullptr;
     float* attn_ws = nullptr;
+    float* attn_ws2 = nullptr;     // split records of the fused single-token attention
     unsigned* attn_counters = nullptr;
     // device-side state of the graph-replayed decode loop
     int* state = nullptr;          // [0] token, [1] position, [2] step
@@ -194,18 +196,10 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
                                                  L.qkv.rows, L.qkv.cols, s));
                 std::swap(res_cur, res_next);
             }
-            TRY(launch_rope(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, 1, 1, c.n_heads, c.n_kv_heads, c.head_dim,
-                            start_pos, pos_dev, c.rope_theta, c.max_seq_len, 1, s));
-            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
-                                 c.head_dim, 1, pos_dev ? 1 : start_pos + 1, c.max_seq_len, pos_dev, D->attn_ws,
-                                 D->attn_counters, s));
-            TRY(launch_quantize_absmax_int8(D->attn_out, D->xq, D->xscale, qdim, s));
-            {
-                const uint8_t* p[1] = {L.o.p};
-                half* y[1] = {D->hidden2};
-                int rows[1] = {L.o.rows};
-                TRY(launch_gemv_int8_packed_multi(1, p, y, rows, L.o.cols, D->xq, D->xscale, s));
-            }
+            TRY(launch_attention_decode(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, c.n_heads,
+                                        c.n_kv_heads, c.head_dim, c.max_seq_len, start_pos, pos_dev, c.rope_theta,
+                                        D->attn_ws2, D->attn_counters, s));
+            TRY(launch_gemv_int8_packed_quant(L.o.p, D->attn_out, D->hidden2, L.o.rows, L.o.cols, s));
             TRY(launch_gemv_int8_packed_norm(L.gate_up.p, D->hidden2, res_cur, L.ffn_norm, res_next, c.rms_norm_eps, gb,
                                              L.gate_up.rows, L.gate_up.cols, s));
             std::swap(res_cur, res_next);
@@ -373,6 +367,7 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     ALLOC(dev_alloc(D, &D->xq, maxdim, true));
     ALLOC(dev_alloc(D, &D->xscale, 4, true));
     ALLOC(dev_alloc(D, &D->attn_ws, attention_workspace_bytes(1, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));
+    ALLOC(dev_alloc(D, &D->attn_ws2, attention_decode_workspace_bytes(c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));
     ALLOC(dev_alloc(D, &D->attn_counters, (size_t)c.n_kv_heads, true));
     ALLOC(dev_alloc(D, &D->state, 4, true));
     D->history_cap = c.max_seq_len;

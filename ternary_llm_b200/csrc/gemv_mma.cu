@@ -57,7 +57,7 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 
 // kI8Norm / kI8Silu: INT8 arithmetic like kI8, but the activation vector is produced inside
 // the kernel's staging phase from FP16 inputs (fused_x.cuh semantics below).
-enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4 };
+enum Mode { kF16B1 = 0, kF16B2 = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4, kI8Quant = 5 };
 
 struct GemvArgs {
     const uint8_t* packed;
@@ -68,6 +68,7 @@ struct GemvArgs {
     // kI8Norm: x = quantise(rmsnorm(fx_a (+ fx_b)) * fx_w); the FP16-rounded sum fx_a + fx_b is
     //          written to fx_res_out by CTA 0 when both are given.
     // kI8Silu: x = quantise(silu(fx_a) * fx_b).
+    // kI8Quant: x = quantise(fx_a).
     const half* fx_a;
     const half* fx_b;
     const half* fx_w;
@@ -299,6 +300,7 @@ __device__ __forceinline__ float cta_max(float v, float* red, int tid)
 //            v = half(a + b) (or a when b is null), var = mean(v^2), o = half(v * rsqrt(var + eps) * w),
 //            scale = absmax(o) / 127 (1 if zero), q = clamp(rint(o * 127 / absmax)).
 //   kI8Silu  "SwiGLU, absmax quantise" (src/transformer.cpp:284-288): o = half(silu(a) * b), then as above.
+//   kI8Quant the quantiser alone (src/transformer.cpp:126-136): o = a.
 // Returns the activation scale.  tmp: half [cols]; red: 33 floats.
 template <int MODE>
 __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, half* tmp, float* red, int tid)
@@ -308,7 +310,7 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, ha
     for (int i = tid; i < n8; i += kThreads) {
         const uint4 ar = *(reinterpret_cast<const uint4*>(a.fx_a) + i);
         uint4 br = make_uint4(0, 0, 0, 0);
-        if (a.fx_b) br = *(reinterpret_cast<const uint4*>(a.fx_b) + i);
+        if (MODE != kI8Quant && a.fx_b) br = *(reinterpret_cast<const uint4*>(a.fx_b) + i);
         const half* ah = reinterpret_cast<const half*>(&ar);
         const half* bh = reinterpret_cast<const half*>(&br);
         uint4 st4;
@@ -319,6 +321,9 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, ha
                 const float g = __half2float(ah[j]);
                 sth[j] = __float2half_rn(g / (1.0f + expf(-g)) * __half2float(bh[j]));
                 mx = fmaxf(mx, fabsf(__half2float(sth[j])));
+            } else if (MODE == kI8Quant) {
+                sth[j] = ah[j];
+                mx = fmaxf(mx, fabsf(__half2float(ah[j])));
             } else {
                 sth[j] = a.fx_b ? __float2half_rn(__half2float(ah[j]) + __half2float(bh[j])) : ah[j];
                 const float v = __half2float(sth[j]);
@@ -409,8 +414,8 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const GemvArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr bool I8 = (MODE == kI8 || MODE == kI8Norm || MODE == kI8Silu);
-    constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu);
+    constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu || MODE == kI8Quant);
+    constexpr bool I8 = (MODE == kI8 || FUSEDX);
     constexpr int LANES = (MODE == kF16B2) ? 32 : 16;
 
     asm volatile("griddepcontrol.launch_dependents;");
@@ -1152,7 +1157,7 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.err = s->misc + 1;
     // shared memory: activations | xfac | partial sums | rings | mbarriers
     size_t xbytes;
-    const bool fusedx = (mode == kI8Norm || mode == kI8Silu);
+    const bool fusedx = (mode == kI8Norm || mode == kI8Silu || mode == kI8Quant);
     if (mode == kI8 || fusedx) xbytes = (size_t)cols;
     else xbytes = (size_t)a.groups * 2 * ((mode == kF16B2) ? 32 : 16) * 16;
     size_t off = (xbytes + 15) & ~(size_t)15;
@@ -1179,6 +1184,7 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
         case kF16B2: return launch_mode<kF16B2>(a, grid, off, stream, s);
         case kI8Norm: return launch_mode<kI8Norm>(a, grid, off, stream, s);
         case kI8Silu: return launch_mode<kI8Silu>(a, grid, off, stream, s);
+        case kI8Quant: return launch_mode<kI8Quant>(a, grid, off, stream, s);
         default: return launch_mode<kI8>(a, grid, off, stream, s);
     }
 }
@@ -1328,6 +1334,12 @@ int launch_gemv_int8_packed_silu(const uint8_t* packed, const half* gate, const 
 {
     const FusedX fx = {gate, up, nullptr, nullptr, 0.f};
     return launch_packed_once(packed, nullptr, y, 1.0f, kI8Silu, 1, rows, cols, stream, nullptr, &fx);
+}
+
+int launch_gemv_int8_packed_quant(const uint8_t* packed, const half* x, half* y, int rows, int cols, cudaStream_t stream)
+{
+    const FusedX fx = {x, nullptr, nullptr, nullptr, 0.f};
+    return launch_packed_once(packed, nullptr, y, 1.0f, kI8Quant, 1, rows, cols, stream, nullptr, &fx);
 }
 
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,

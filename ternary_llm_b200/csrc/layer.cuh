@@ -33,4 +33,11 @@ int launch_attention(const half* q, const half* k_cache, const half* v_cache, ha
                      int n_kv_heads, int head_dim, int seq_len, int kv_len, int kv_len_max, const int* kv_len_dev,
                      float* ws, unsigned* counters, cudaStream_t stream);
 
+// Single-token step: RoPE + cache append + attention in one launch (q is read unrotated and not
+// modified; the rotated key and the value go to cache position pos, or *pos_dev).
+size_t attention_decode_workspace_bytes(int n_heads, int n_kv_heads, int head_dim, int kv_len_max);
+int launch_attention_decode(half* q, const half* k, const half* v, half* k_cache, half* v_cache, half* out, int n_heads,
+                            int n_kv_heads, int head_dim, int kv_len_max, int pos, const int* pos_dev, float theta,
+                            float* ws, unsigned* counters, cudaStream_t stream);
+
 }  // namespace tllm
