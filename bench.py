@@ -580,6 +580,8 @@ def run_ours(args):
                              "peak_tflops": measured_peak_bf16(), "peak_kind": "measured bf16 cuBLAS burst",
                              "rows": gemm_rows},
         }
+        if world == 1 and not args.no_decode:
+            out["decode"] = decode_sample(torch, tl, dev)
         if world == 1 and not args.no_cpu:
             v, dt, kind, what = cpu_layer_sample(reps=3, threads=os.cpu_count() or 1)
             out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind,
@@ -587,6 +589,40 @@ def run_ours(args):
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+DECODE_ARCH_1B = dict(vocab_size=128256, hidden_dim=2048, intermediate_dim=8192, n_layers=16, n_heads=32, n_kv_heads=8,
+                      head_dim=64, max_seq_len=1024, rope_theta=500000.0, rms_norm_eps=1e-5)
+
+
+def decode_sample(torch, tl, dev, n_prompt=512, n_steps=128):
+    """Decode tok/s of the library's decoder on the benchmark's 1B architecture (16 layers, hidden
+    2048, 32/8 heads of 64, intermediate 8192, vocab 128256, FP16 embedding and lm_head) with seeded
+    random weights: a 512-token prefill, then 128 greedy steps replayed as one CUDA graph per step
+    (position, token and activation scales stay on the device).  Reported beside the headline."""
+    from ternary_llm_b200 import tllm_format as tf
+    cfg = tf.TllmConfig(**DECODE_ARCH_1B)
+    dec = tl.Decoder(tf.random_model(cfg, seed=2026), int8_decode=True)
+    prompt = torch.from_numpy(np.random.default_rng(0).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)).to(dev)
+    logits = dec.forward(prompt, 0)
+    first = int(logits.float().argmax().item())
+    dec.generate(first, n_prompt, 4)             # captures the step graph
+    dec.reset()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    dec.forward(prompt, 0)
+    e1.record()
+    torch.cuda.synchronize()
+    _, ms = dec.generate(first, n_prompt, n_steps)
+    tl.check_device_errors()
+    dec.close()
+    layer_bytes = sum(gemv_bytes(o, i) for _, o, i in cfg.proj_shapes())
+    step_bytes = layer_bytes * cfg.n_layers + cfg.vocab_size * cfg.hidden_dim * 2
+    return {"workload": "LLaMA-3.2-1B architecture, seeded random weights, 512-token prefill then 128 greedy steps, batch 1",
+            "prefill_ms": e0.elapsed_time(e1), "decode_ms_per_token": ms, "tok_per_s": 1e3 / ms,
+            "weight_bytes_per_token": step_bytes, "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9,
+            "launches_per_token": cfg.n_layers * 5 + 5,
+            "arithmetic": "INT8 activations for single-token steps (the reference engine's choice), FP16 + tcgen05 GEMM for the prefill"}
 
 
 def run_case(args):
@@ -628,8 +664,7 @@ def run_case(args):
         # decode:ARCH[:prompt[:steps[:eager]]] -- the library's decoder on a seeded random model of
         # the benchmark's 1B architecture (`1b`, 16 layers) or a 4-layer cut of it (`1b-4l`)
         from ternary_llm_b200 import tllm_format as tf
-        arch = dict(vocab_size=128256, hidden_dim=2048, intermediate_dim=8192, n_layers=16, n_heads=32, n_kv_heads=8,
-                    head_dim=64, max_seq_len=1024, rope_theta=500000.0, rms_norm_eps=1e-5)
+        arch = dict(DECODE_ARCH_1B)
         if dims == "1b-4l":
             arch.update(n_layers=4, vocab_size=32000)
         elif dims != "1b":
@@ -676,6 +711,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decoder tok/s sample (N=1 only)")
     ap.add_argument("--layers", type=int, default=0, help="N>1 only: layer count override for quick checks (0 = the full 80)")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")

@@ -324,6 +324,7 @@ attention_decode_kernel(const DecodeArgs a)
 {
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
+    TL_MARK(20, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, hp = hd >> 1;
     const int G = a.n_heads / a.n_kv_heads;
@@ -357,6 +358,7 @@ attention_decode_kernel(const DecodeArgs a)
     __syncthreads();
 
     pdl_wait();
+    TL_MARK(20, 1);
     const int pos = a.pos_dev ? *a.pos_dev : a.pos;
     const int limit = pos + 1;
     int nactive = (limit + kDecChunk - 1) / kDecChunk;
@@ -432,40 +434,36 @@ attention_decode_kernel(const DecodeArgs a)
             if (tid == 0 && a.err) atomicExch(a.err, TLLM_ERR_TIMEOUT);
             return;
         }
-        // ---- scores: thread j <-> position c0 + j ----------------------------------
-        if (tid < nc) {
-            float dot[kAttnMaxGroup];
-#pragma unroll
-            for (int g = 0; g < kAttnMaxGroup; g++) dot[g] = 0.f;
-            const uint4* k4 = reinterpret_cast<const uint4*>(ks + (size_t)tid * hd);
-            const int nd8 = hd >> 3;
-            int d8 = tid % nd8;
-            for (int i8 = 0; i8 < nd8; i8++) {
-                const uint4 raw = k4[d8];
-                const half2* h = reinterpret_cast<const half2*>(&raw);
-                float kf[8];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float2 f = __half22float2(h[j]);
-                    kf[2 * j] = f.x;
-                    kf[2 * j + 1] = f.y;
-                }
-#pragma unroll
-                for (int g = 0; g < kAttnMaxGroup; g++) {
-                    if (g < G) {
-                        const float4 q0 = *reinterpret_cast<const float4*>(qs + g * hd + d8 * 8);
-                        const float4 q1 = *reinterpret_cast<const float4*>(qs + g * hd + d8 * 8 + 4);
-                        dot[g] += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x +
-                                  kf[5] * q1.y + kf[6] * q1.z + kf[7] * q1.w;
+        TL_MARK(20, 3);
+        // ---- scores: thread <-> (position group, head g, 8-channel piece c) -------------
+        // The thread keeps its piece of the (rotated, scaled) query in registers and walks the
+        // positions of its group: one 16-byte K load and 8 FMAs per position, then the pieces of
+        // a row are added with shuffles.  The lanes of a piece group read one full K row.
+        {
+            const int cpr = hd >> 3;                       // pieces per row (4, 8 or 16)
+            const int tpg = G * cpr;                       // threads per position group
+            const int c = tid % cpr, g = (tid / cpr) % G, pgp = tid / tpg, npg = kAttnThreads / tpg;
+            if (pgp < npg) {
+                const float4 q0 = *reinterpret_cast<const float4*>(qs + g * hd + c * 8);
+                const float4 q1 = *reinterpret_cast<const float4*>(qs + g * hd + c * 8 + 4);
+                for (int j0 = 0; j0 < nc; j0 += npg) {
+                    const int j = j0 + pgp;
+                    float dot = 0.f;
+                    if (j < nc) {
+                        const uint4 raw = *(reinterpret_cast<const uint4*>(ks + (size_t)j * hd) + c);
+                        const half2* h = reinterpret_cast<const half2*>(&raw);
+                        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]);
+                        const float2 f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+                        dot = (f0.x * q0.x + f0.y * q0.y) + (f1.x * q0.z + f1.y * q0.w) +
+                              (f2.x * q1.x + f2.y * q1.y) + (f3.x * q1.z + f3.y * q1.w);
                     }
+                    for (int o2 = cpr >> 1; o2 > 0; o2 >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
+                    if (c == 0 && j < nc) ps[g * kDecChunk + j] = dot;
                 }
-                d8 = (d8 + 1 == nd8) ? 0 : d8 + 1;
             }
-#pragma unroll
-            for (int g = 0; g < kAttnMaxGroup; g++)
-                if (g < G) ps[g * kDecChunk + tid] = dot[g];
         }
         __syncthreads();
+        TL_MARK(20, 4);
         for (int g = warp; g < G; g += kAttnThreads / 32) {
             float* p = ps + g * kDecChunk;
             float mx = -FLT_MAX;
@@ -488,6 +486,7 @@ attention_decode_kernel(const DecodeArgs a)
             }
         }
         __syncthreads();
+        TL_MARK(20, 5);
         // ---- P.V: thread <-> (head, channel pair) x position group ---------------------
         if (pgroups > 1) {
             const int item = tid % items, pg = tid / items;
@@ -496,12 +495,28 @@ attention_decode_kernel(const DecodeArgs a)
                 const float* p = ps + g * kDecChunk;
                 const half2* vp = reinterpret_cast<const half2*>(vs) + pr;
                 float2 acc = make_float2(o[0].x * corr[g], o[0].y * corr[g]);
-                for (int j = pg; j < nc; j += pgroups) {
+                float2 acc1 = make_float2(0.f, 0.f), acc2 = acc1, acc3 = acc1;
+                int j = pg;
+                for (; j + 3 * pgroups < nc; j += 4 * pgroups) {
+                    const half2 h0 = vp[(size_t)j * hp], h1 = vp[(size_t)(j + pgroups) * hp];
+                    const half2 h2 = vp[(size_t)(j + 2 * pgroups) * hp], h3 = vp[(size_t)(j + 3 * pgroups) * hp];
+                    const float p0 = p[j], p1 = p[j + pgroups], p2 = p[j + 2 * pgroups], p3 = p[j + 3 * pgroups];
+                    const float2 v0 = __half22float2(h0), v1 = __half22float2(h1), v2 = __half22float2(h2), v3 = __half22float2(h3);
+                    acc.x = fmaf(p0, v0.x, acc.x);
+                    acc.y = fmaf(p0, v0.y, acc.y);
+                    acc1.x = fmaf(p1, v1.x, acc1.x);
+                    acc1.y = fmaf(p1, v1.y, acc1.y);
+                    acc2.x = fmaf(p2, v2.x, acc2.x);
+                    acc2.y = fmaf(p2, v2.y, acc2.y);
+                    acc3.x = fmaf(p3, v3.x, acc3.x);
+                    acc3.y = fmaf(p3, v3.y, acc3.y);
+                }
+                for (; j < nc; j += pgroups) {
                     const float2 vv = __half22float2(vp[(size_t)j * hp]);
                     acc.x = fmaf(p[j], vv.x, acc.x);
                     acc.y = fmaf(p[j], vv.y, acc.y);
                 }
-                o[0] = acc;
+                o[0] = make_float2((acc.x + acc1.x) + (acc2.x + acc3.x), (acc.y + acc1.y) + (acc2.y + acc3.y));
             }
         } else {
 #pragma unroll
@@ -512,18 +527,28 @@ attention_decode_kernel(const DecodeArgs a)
                     const float* p = ps + g * kDecChunk;
                     const half2* vp = reinterpret_cast<const half2*>(vs) + pr;
                     float2 acc = make_float2(o[e].x * corr[g], o[e].y * corr[g]);
-                    for (int j = 0; j < nc; j++) {
+                    float2 acc1 = make_float2(0.f, 0.f);
+                    int j = 0;
+                    for (; j + 1 < nc; j += 2) {
+                        const float2 v0 = __half22float2(vp[(size_t)j * hp]), v1 = __half22float2(vp[(size_t)(j + 1) * hp]);
+                        acc.x = fmaf(p[j], v0.x, acc.x);
+                        acc.y = fmaf(p[j], v0.y, acc.y);
+                        acc1.x = fmaf(p[j + 1], v1.x, acc1.x);
+                        acc1.y = fmaf(p[j + 1], v1.y, acc1.y);
+                    }
+                    if (j < nc) {
                         const float2 vv = __half22float2(vp[(size_t)j * hp]);
                         acc.x = fmaf(p[j], vv.x, acc.x);
                         acc.y = fmaf(p[j], vv.y, acc.y);
                     }
-                    o[e] = acc;
+                    o[e] = make_float2(acc.x + acc1.x, acc.y + acc1.y);
                 }
             }
         }
         __syncthreads();
     }
 
+    TL_MARK(20, 2);
     // ---- reduce the position groups, then write or publish ------------------------------
     if (pgroups > 1) {
         const int item = tid % items, pg = tid / items;
@@ -557,6 +582,7 @@ attention_decode_kernel(const DecodeArgs a)
         }
     }
     if (nactive == 1) return;
+    TL_MARK(20, 6);
     if (tid < G) {
         my[G * hd + tid] = m_run[tid];
         my[G * hd + G + tid] = l_run[tid];
@@ -584,6 +610,7 @@ attention_decode_kernel(const DecodeArgs a)
         }
         op[idx] = __float2half_rn(den > 0.f ? num / den : 0.f);
     }
+    TL_MARK(20, 7);
 }
 
 size_t attention_decode_workspace_bytes(int n_heads, int n_kv_heads, int head_dim, int kv_len_max)
@@ -603,7 +630,8 @@ int launch_attention_decode(half* q, const half* k, const half* v, half* k_cache
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(TLLM_ERR_SHAPE, "attention: n_heads=%d n_kv_heads=%d", n_heads, n_kv_heads);
     const int G = n_heads / n_kv_heads;
     const int items = G * head_dim / 2;
-    if (G > kAttnMaxGroup || head_dim % 8 || head_dim > 128 || head_dim / 2 > kAttnThreads ||
+    const int cpr = head_dim / 8;
+    if (G > kAttnMaxGroup || head_dim % 8 || head_dim > 128 || (cpr & (cpr - 1)) || cpr < 2 || G * cpr > kAttnThreads ||
         items > kDecMaxItems * kAttnThreads || G * head_dim / 2 > 4 * kAttnThreads)
         return fail(TLLM_ERR_SHAPE, "attention: head_dim=%d with %d heads per group is not supported", head_dim, G);
     if (!pos_dev && (pos < 0 || pos >= kv_len_max)) return fail(TLLM_ERR_SHAPE, "attention: pos=%d kv_len_max=%d", pos, kv_len_max);
@@ -693,3 +721,5 @@ int launch_attention(const half* q, const half* k_cache, const half* v_cache, ha
 }
 
 }  // namespace tllm
+
+TL_DUMP(tllm_b200_debug_timeline_attention)

@@ -38,6 +38,7 @@
 
 #include "common.cuh"
 #include "packed_layout.cuh"
+#include "launch.cuh"
 
 namespace tllm {
 
@@ -420,6 +421,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
 
     asm volatile("griddepcontrol.launch_dependents;");
     PHASE(0);
+    TL_MARK(MODE, 0);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.groups;
@@ -466,6 +468,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     PHASE(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     PHASE(2);
+    TL_MARK(MODE, 1);
 
     float fused_scale = 1.0f;
     if (FUSEDX) {
@@ -480,6 +483,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     }
     __syncthreads();
     PHASE(3);
+    TL_MARK(MODE, 2);
 
     // ---- per-lane constants ------------------------------------------------------
     const int t = lane & 3, gq = lane >> 2;
@@ -581,6 +585,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     if (dirty) flush();
     if (!ok && lane == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
     PHASE(4);
+    TL_MARK(MODE, 3);
     __syncthreads();
     PHASE(5);
 
@@ -1594,3 +1599,5 @@ int weight_unregister(const void* nz)
 }
 
 }  // namespace tllm
+
+TL_DUMP(tllm_b200_debug_timeline_gemv)
