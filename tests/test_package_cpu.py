@@ -95,6 +95,36 @@ def test_argument_errors_need_no_gpu():
     assert b"cols" in h.tllm_b200_last_error() or b"M=" in h.tllm_b200_last_error()
 
 
+def test_layer_argument_errors_need_no_gpu():
+    h = tl.lib()
+    buf = ctypes.create_string_buffer(4096 + 64)
+    p = (ctypes.addressof(buf) + 63) & ~63
+    assert h.tllm_b200_rmsnorm(None, p, p, None, None, 1, 128, 1e-5, None) == -1
+    assert h.tllm_b200_rmsnorm(p, p, p, None, None, 1, 0, 1e-5, None) == -3
+    assert h.tllm_b200_rope(p, None, 1, 1, 4, 2, 64, 0, 10000.0, None) == -1
+    assert h.tllm_b200_rope(p, p, 1, 1, 4, 2, 63, 0, 10000.0, None) == -3            # odd head_dim
+    assert h.tllm_b200_attention(p, p, p, None, 1, 4, 2, 64, 1, 1, 8, None) == -1
+    assert h.tllm_b200_attention(p, p, p, p, 1, 0, 2, 64, 1, 1, 8, None) == -3
+    assert h.tllm_b200_silu_mul(p, p, p, -1, None) == -3
+    assert h.tllm_b200_add(p + 2, p, p, 8, None) == -2
+    assert h.tllm_b200_fp16_gemv(p, p, p, 4, 0, None) == -3
+    assert h.tllm_b200_embedding_lookup(p, None, p, 1, 8, None) == -1
+    assert h.tllm_b200_decoder_create(None, 0, None) == -1
+    assert h.tllm_b200_decoder_reset(None, None) == -1
+    assert h.tllm_b200_decoder_generate(None, 0, 0, 1, None, None) == -1
+    tables = (ctypes.c_void_p * 1)(p)
+    rows = (ctypes.c_int * 1)(16)
+    assert h.tllm_b200_gemv_int8_packed_multi(5, tables, tables, rows, 128, p, p, None) == -5
+    assert h.tllm_b200_gemv_int8_packed_multi(1, tables, tables, rows, 100, p, p, None) == -3
+    # a model description with an unsupported group size is refused before anything is allocated
+    d = _lib.ModelDesc()
+    layers = (_lib.LayerWeightsDesc * 1)()
+    d.layers, d.embedding_table, d.final_norm_weight = layers, p, p
+    d.group_size, d.n_layers = 64, 1
+    out = ctypes.c_void_p()
+    assert h.tllm_b200_decoder_create(ctypes.byref(d), 0, ctypes.byref(out)) == -4
+
+
 def test_ops_refuse_cpu_tensors():
     import torch
     a = torch.zeros(16, 4, dtype=torch.int32)
