@@ -258,6 +258,15 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
     }
 }
 
+// INT8 activations in shared memory are permuted so that the eight B words a lane needs for
+// one scale group (k32 step m, half h: original word 8m + 4h + t of the group's 32) are
+// contiguous: slot of original word w = group * 32 + t * 8 + 2m + h.
+__device__ __forceinline__ int int8_word_slot(int w)
+{
+    const int g = w >> 5, r = w & 31;
+    return (g << 5) + ((r & 3) << 3) + ((r >> 3) << 1) + ((r >> 2) & 1);
+}
+
 // Block-wide reductions over the CTA's kWarps warps; `red` is 33 floats of shared memory.
 __device__ __forceinline__ float cta_sum(float v, float* red, int tid)
 {
@@ -366,7 +375,8 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, ha
             }
             w[h] = acc;
         }
-        *(reinterpret_cast<uint2*>(xq) + i) = make_uint2(w[0], w[1]);
+        reinterpret_cast<uint32_t*>(xq)[int8_word_slot(2 * i)] = w[0];
+        reinterpret_cast<uint32_t*>(xq)[int8_word_slot(2 * i + 1)] = w[1];
     }
     return (absmax > 0.f) ? (absmax / 127.0f) : 1.0f;
 }
@@ -374,7 +384,7 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, ha
 // One tile (one scale group of a 16-row block): four k32 MMA steps.  Returns the
 // weighted integer group sums of rows gq (p0) and gq+8 (p1).
 //   xq4: FP16 modes, this lane's 128-bit B words of the group (step pairs at [0], [LANES])
-//   xw : INT8 mode, the group's 32 activation words offset by t
+//   xw : INT8 mode, this lane's eight B words of the group (int8_word_slot order), 32-byte aligned
 template <bool I8, int LANES>
 __device__ __forceinline__ void tile_mma(const uint8_t* tp, int lane, const uint4* xq4, const uint32_t* xw,
                                          int mulA, int mulB, int& p0, int& p1)
@@ -383,8 +393,8 @@ __device__ __forceinline__ void tile_mma(const uint8_t* tp, int lane, const uint
     const uint2 cb = *reinterpret_cast<const uint2*>(tp + 256 + lane * 8);
     uint4 b01, b23;
     if (I8) {
-        b01 = make_uint4(xw[0], xw[4], xw[8], xw[12]);
-        b23 = make_uint4(xw[16], xw[20], xw[24], xw[28]);
+        b01 = *reinterpret_cast<const uint4*>(xw);
+        b23 = *reinterpret_cast<const uint4*>(xw + 4);
     } else {
         b01 = xq4[0];
         b23 = xq4[LANES];
@@ -404,8 +414,14 @@ __device__ __forceinline__ void tile_mma(const uint8_t* tp, int lane, const uint
         imma<I8, true>(d, prmt(kTabA_lo, kTabA_hi, s0), prmt(kTabA_lo, kTabA_hi, s1),
                        prmt(kTabB_lo, kTabB_hi, s0), prmt(kTabB_lo, kTabB_hi, s1), b23.z, b23.w);
     }
-    p0 = d[1] * mulA + d[0] * mulB;
-    p1 = d[3] * mulA + d[2] * mulB;
+    if (I8) {
+        // every B column carries the same vector, so every accumulator column holds the sum
+        p0 = d[0];
+        p1 = d[2];
+    } else {
+        p0 = d[1] * mulA + d[0] * mulB;
+        p1 = d[3] * mulA + d[2] * mulB;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -477,7 +493,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     } else if (I8) {
         const int n16 = a.cols / 16;
         const uint4* src = reinterpret_cast<const uint4*>(a.x);
-        for (int i = tid; i < n16; i += kThreads) reinterpret_cast<uint4*>(xstage)[i] = __ldg(src + i);
+        for (int i = tid; i < n16; i += kThreads) {
+            const uint4 v = __ldg(src + i);
+            xstage[int8_word_slot(4 * i)] = v.x;
+            xstage[int8_word_slot(4 * i + 1)] = v.y;
+            xstage[int8_word_slot(4 * i + 2)] = v.z;
+            xstage[int8_word_slot(4 * i + 3)] = v.w;
+        }
     } else {
         stage_x_f16<LANES>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xfac, tid);
     }
@@ -498,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     }
     const float* xf = xfac + ((MODE == kF16B2) ? (t >> 1) : 0) * G;
     const uint4* xq4 = reinterpret_cast<const uint4*>(xstage) + ((LANES == 32) ? lane : (lane & 15));
-    const uint32_t* xw = xstage + t;
+    const uint32_t* xw = xstage + t * 8;
 
     // ---- main loop: this warp's tiles, four per ring slot --------------------------
     int rb = (int)((unsigned)w0 / (unsigned)G);
@@ -508,9 +530,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     bool dirty = false, ok = true;
 
     auto flush = [&]() {
-        // lanes t and t^1 hold the two digit halves of one vector
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        if (!I8) {       // lanes t and t^1 hold the two digit halves of one vector
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        }
         float* pu = part + seg * 32;
         if (I8 || MODE == kF16B1) {
             if (t == 0) {
