@@ -434,7 +434,6 @@ attention_decode_kernel(const DecodeArgs a)
             if (tid == 0 && a.err) atomicExch(a.err, TLLM_ERR_TIMEOUT);
             return;
         }
-        TL_MARK(20, 3);
         // ---- scores: thread <-> (position group, head g, 8-channel piece c) -------------
         // The thread keeps its piece of the (rotated, scaled) query in registers and walks the
         // positions of its group: one 16-byte K load and 8 FMAs per position, then the pieces of
@@ -443,27 +442,42 @@ attention_decode_kernel(const DecodeArgs a)
             const int cpr = hd >> 3;                       // pieces per row (4, 8 or 16)
             const int tpg = G * cpr;                       // threads per position group
             const int c = tid % cpr, g = (tid / cpr) % G, pgp = tid / tpg, npg = kAttnThreads / tpg;
-            if (pgp < npg) {
+            const bool act = pgp < npg;               // threads beyond the last whole group only take part in the shuffles
+            {
                 const float4 q0 = *reinterpret_cast<const float4*>(qs + g * hd + c * 8);
                 const float4 q1 = *reinterpret_cast<const float4*>(qs + g * hd + c * 8 + 4);
-                for (int j0 = 0; j0 < nc; j0 += npg) {
-                    const int j = j0 + pgp;
-                    float dot = 0.f;
-                    if (j < nc) {
-                        const uint4 raw = *(reinterpret_cast<const uint4*>(ks + (size_t)j * hd) + c);
-                        const half2* h = reinterpret_cast<const half2*>(&raw);
-                        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]);
-                        const float2 f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-                        dot = (f0.x * q0.x + f0.y * q0.y) + (f1.x * q0.z + f1.y * q0.w) +
-                              (f2.x * q1.x + f2.y * q1.y) + (f3.x * q1.z + f3.y * q1.w);
+                auto piece = [&](int j) -> float {        // this thread's 8 channels of position j
+                    if (!act || j >= nc) return 0.f;
+                    const uint4 raw = *(reinterpret_cast<const uint4*>(ks + (size_t)j * hd) + c);
+                    const half2* h = reinterpret_cast<const half2*>(&raw);
+                    const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]);
+                    const float2 f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+                    return (f0.x * q0.x + f0.y * q0.y) + (f1.x * q0.z + f1.y * q0.w) +
+                           (f2.x * q1.x + f2.y * q1.y) + (f3.x * q1.z + f3.y * q1.w);
+                };
+                // four positions per trip: their loads and shuffle chains are independent
+                // (the trip count must not depend on the position group: lanes of several groups can
+                // share a warp and the shuffles below name all 32 lanes)
+                for (int jb = 0; jb < nc; jb += 4 * npg) {
+                    const int j0 = jb + pgp;
+                    float d0 = piece(j0), d1 = piece(j0 + npg), d2 = piece(j0 + 2 * npg), d3 = piece(j0 + 3 * npg);
+                    for (int o2 = cpr >> 1; o2 > 0; o2 >>= 1) {
+                        d0 += __shfl_xor_sync(0xffffffffu, d0, o2);
+                        d1 += __shfl_xor_sync(0xffffffffu, d1, o2);
+                        d2 += __shfl_xor_sync(0xffffffffu, d2, o2);
+                        d3 += __shfl_xor_sync(0xffffffffu, d3, o2);
                     }
-                    for (int o2 = cpr >> 1; o2 > 0; o2 >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
-                    if (c == 0 && j < nc) ps[g * kDecChunk + j] = dot;
+                    if (c == 0 && act) {
+                        float* pg_ = ps + g * kDecChunk;
+                        if (j0 < nc) pg_[j0] = d0;
+                        if (j0 + npg < nc) pg_[j0 + npg] = d1;
+                        if (j0 + 2 * npg < nc) pg_[j0 + 2 * npg] = d2;
+                        if (j0 + 3 * npg < nc) pg_[j0 + 3 * npg] = d3;
+                    }
                 }
             }
         }
         __syncthreads();
-        TL_MARK(20, 4);
         for (int g = warp; g < G; g += kAttnThreads / 32) {
             float* p = ps + g * kDecChunk;
             float mx = -FLT_MAX;
@@ -486,7 +500,6 @@ attention_decode_kernel(const DecodeArgs a)
             }
         }
         __syncthreads();
-        TL_MARK(20, 5);
         // ---- P.V: thread <-> (head, channel pair) x position group ---------------------
         if (pgroups > 1) {
             const int item = tid % items, pg = tid / items;
@@ -582,7 +595,6 @@ attention_decode_kernel(const DecodeArgs a)
         }
     }
     if (nactive == 1) return;
-    TL_MARK(20, 6);
     if (tid < G) {
         my[G * hd + tid] = m_run[tid];
         my[G * hd + G + tid] = l_run[tid];
@@ -600,17 +612,34 @@ attention_decode_kernel(const DecodeArgs a)
     const float* base = a.ws + (size_t)kvh * a.nsplit * rec;
     for (int idx = tid; idx < G * hd; idx += kAttnThreads) {
         const int g = idx / hd;
-        float m = -FLT_MAX;
-        for (int sidx = 0; sidx < nactive; sidx++) m = fmaxf(m, __ldcg(base + (size_t)sidx * rec + G * hd + g));
-        float num = 0.f, den = 0.f;
-        for (int sidx = 0; sidx < nactive; sidx++) {
-            const float w = __expf(__ldcg(base + (size_t)sidx * rec + G * hd + g) - m);
-            num = fmaf(w, __ldcg(base + (size_t)sidx * rec + idx), num);
-            den = fmaf(w, __ldcg(base + (size_t)sidx * rec + G * hd + G + g), den);
+        float m = -FLT_MAX, num = 0.f, den = 0.f;
+        for (int s0 = 0; s0 < nactive; s0 += 8) {
+            // issue every load of up to eight splits before any of them is used
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const bool live = s0 + u < nactive;
+                const float* r = base + (size_t)(live ? s0 + u : s0) * rec;
+                ms[u] = live ? __ldcg(r + G * hd + g) : -FLT_MAX;
+                ls[u] = live ? __ldcg(r + G * hd + G + g) : 0.f;
+                os[u] = live ? __ldcg(r + idx) : 0.f;
+            }
+            float mx = m;
+#pragma unroll
+            for (int u = 0; u < 8; u++) mx = fmaxf(mx, ms[u]);
+            const float c0 = __expf(m - mx);              // rescale what earlier trips accumulated
+            num *= c0;
+            den *= c0;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float w = __expf(ms[u] - mx);      // 0 for the padding entries
+                num = fmaf(w, os[u], num);
+                den = fmaf(w, ls[u], den);
+            }
+            m = mx;
         }
         op[idx] = __float2half_rn(den > 0.f ? num / den : 0.f);
     }
-    TL_MARK(20, 7);
 }
 
 size_t attention_decode_workspace_bytes(int n_heads, int n_kv_heads, int head_dim, int kv_len_max)
