@@ -76,6 +76,12 @@ struct GemvArgs {
     half* fx_res_out;
     float fx_eps;
     int off_xtmp;           // shared memory: half [cols] staging + 64 floats of reduction scratch
+    // Several matrices packed back to back and streamed as one (q|k|v, gate|up): row r of the
+    // concatenation belongs to segment i with seg_row[i] <= r < seg_row[i + 1] and is written
+    // to seg_y[i][r - seg_row[i]].  nseg == 0: one matrix, output y.
+    int nseg;
+    int seg_row[TLLM_MAX_FUSED + 1];
+    half* seg_y[TLLM_MAX_FUSED];
     int rows, cols, groups; // groups = cols / 128 = tiles per row block
     int batch;              // 1 or 2 vectors handled by this launch
     int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
@@ -424,6 +430,17 @@ __device__ __forceinline__ void tile_mma(const uint8_t* tp, int lane, const uint
     }
 }
 
+// Address of output element (vector b, row r) -- see GemvArgs::nseg.
+__device__ __forceinline__ half* out_ptr(const GemvArgs& a, int b, int r)
+{
+    if (a.nseg == 0) return a.y + (size_t)b * a.rows + r;
+    int i = 0;
+#pragma unroll
+    for (int k = 1; k < TLLM_MAX_FUSED; k++)
+        if (k < a.nseg && r >= a.seg_row[k]) i = k;
+    return a.seg_y[i] + (size_t)b * (a.seg_row[i + 1] - a.seg_row[i]) + (r - a.seg_row[i]);
+}
+
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
@@ -681,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
         const bool full = (tb - ta == G);
         const int r = r_b * 16 + row;
         if (full) {
-            if (r < a.rows && b < nb) a.y[(size_t)b * a.rows + r] = __float2half_rn(s * oscale);
+            if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(s * oscale);
         } else {
             // this row block is shared with neighbouring CTAs: publish the partial sums;
             // the contributor that arrives last adds all records in CTA order
@@ -707,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
                     const int c_rb = (int)((unsigned)part_start(c, a.part_q, a.part_r) / (unsigned)G);
                     tot += __ldcg(a.ws + (size_t)c * 64 + ((r_b == c_rb) ? 0 : 32) + lane);
                 }
-                if (r < a.rows && b < nb) a.y[(size_t)b * a.rows + r] = __float2half_rn(tot * oscale);
+                if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(tot * oscale);
                 if (lane == 0) a.counters[r_b] = 0;
             }
         }
@@ -1121,6 +1138,12 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
 }
 
 // x: half [batch, cols] (mode f16) or int8 [cols]; batch 1..2 per launch.
+struct SegY {
+    int n;
+    int rows[TLLM_MAX_FUSED];
+    half* y[TLLM_MAX_FUSED];
+};
+
 struct FusedX {
     const half* a;
     const half* b;
@@ -1131,7 +1154,7 @@ struct FusedX {
 
 static int launch_packed_once(const uint8_t* packed, const void* x, half* y, float in_scale, int mode,
                               int batch, int rows, int cols, cudaStream_t stream, const float* in_scale_dev = nullptr,
-                              const FusedX* fx = nullptr)
+                              const FusedX* fx = nullptr, const SegY* seg = nullptr)
 {
     DeviceScratch* s = nullptr;
     int st = get_scratch(&s);
@@ -1142,6 +1165,16 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.y = y;
     a.in_scale = in_scale;
     a.in_scale_dev = in_scale_dev;
+    if (seg) {
+        a.nseg = seg->n;
+        int r0 = 0;
+        for (int i = 0; i < seg->n; i++) {
+            a.seg_row[i] = r0;
+            a.seg_y[i] = seg->y[i];
+            r0 += seg->rows[i];
+        }
+        for (int i = seg->n; i <= TLLM_MAX_FUSED; i++) a.seg_row[i] = r0;
+    }
     if (fx) {
         a.fx_a = fx->a;
         a.fx_b = fx->b;
@@ -1309,6 +1342,24 @@ static int gemv_packed_multi_any(int count, const uint8_t* const* packed, half* 
     int st = get_scratch(&s);
     if (st) return st;
     const bool i8 = (xq != nullptr);
+    // Matrices that were packed back to back (every row count but the last a multiple of 16)
+    // are one contiguous tile array: stream them as one matrix, outputs scattered per segment.
+    if (count >= 2 && count <= TLLM_MAX_FUSED) {
+        bool contiguous = true;
+        SegY seg = {};
+        seg.n = count;
+        int total = 0;
+        for (int i = 0; i < count; i++) {
+            if (i + 1 < count)
+                contiguous = contiguous && (rows[i] % 16 == 0) && (packed[i + 1] == packed[i] + packed_bytes(rows[i], cols));
+            seg.rows[i] = rows[i];
+            seg.y[i] = y[i];
+            total += rows[i];
+        }
+        if (contiguous)
+            return i8 ? launch_packed_once(packed[0], xq, nullptr, 1.0f, kI8, 1, total, cols, stream, scale_dev, nullptr, &seg)
+                      : launch_packed_once(packed[0], x, nullptr, 1.0f, kF16B1, 1, total, cols, stream, nullptr, nullptr, &seg);
+    }
     // One fused launch pays off when some matrix alone cannot fill the SMs with whole row
     // blocks (k and v of grouped-query attention); matrices that can are streamed one by
     // one by the general kernel, which is the faster of the two for them.

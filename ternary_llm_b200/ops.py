@@ -100,7 +100,9 @@ class PreparedWeight:
     tensors use the packed copy, as the C++ engine integration does."""
 
     def __init__(self, nonzero_masks, sign_masks, scales, rows: int, cols: int, register: bool = True,
-                 keep_source: bool = True):
+                 keep_source: bool = True, storage=None):
+        """storage: a uint8 CUDA tensor (view) of packed_bytes(rows, cols) bytes to pack into
+        instead of a fresh allocation -- see prepare_group."""
         nz, sg, sc = _weights(nonzero_masks, sign_masks, scales)
         self.rows, self.cols = rows, cols
         if register and not keep_source:
@@ -111,7 +113,11 @@ class PreparedWeight:
         nbytes = packed_bytes(rows, cols)
         if nbytes == 0:
             raise ValueError(f"unsupported shape rows={rows} cols={cols}")
-        self.packed = torch.empty(nbytes, dtype=torch.uint8, device=nonzero_masks.device)
+        if storage is None:
+            storage = torch.empty(nbytes, dtype=torch.uint8, device=nonzero_masks.device)
+        elif storage.numel() != nbytes or storage.dtype != torch.uint8 or not storage.is_contiguous():
+            raise ValueError(f"storage must be a contiguous uint8 tensor of {nbytes} bytes")
+        self.packed = storage
         _lib.check(_lib.lib().tllm_b200_weight_prepare(nz, sg, sc, rows, cols, GROUP_SIZE,
                                                        self.packed.data_ptr(), nbytes, _stream()))
         self.registered = False
@@ -139,6 +145,21 @@ class PreparedWeight:
             self.release()
         except Exception:
             pass
+
+
+def prepare_group(weights, register: bool = False, keep_source: bool = False):
+    """Packs several matrices that share their input vector (q, k, v; gate, up) back to back
+    in one allocation.  weights: list of (nonzero_masks, sign_masks, scales, rows, cols).
+    ternary_gemv_packed_multi on the returned list streams them as ONE matrix in a single
+    launch (every row count but the last must be a multiple of 16 for that)."""
+    sizes = [packed_bytes(r, c) for (_, _, _, r, c) in weights]
+    buf = torch.empty(sum(sizes), dtype=torch.uint8, device=weights[0][0].device)
+    out, off = [], 0
+    for (nz, sg, sc, r, c), n in zip(weights, sizes):
+        out.append(PreparedWeight(nz, sg, sc, r, c, register=register, keep_source=keep_source or register,
+                                  storage=buf[off:off + n]))
+        off += n
+    return out
 
 
 def ternary_gemv_packed(w: PreparedWeight, input, output, batch: int = 1) -> None:

@@ -234,3 +234,36 @@ def test_tllm_file_to_prepared_weights(tmp_path):
             y = _run_packed(w, x)
             y64, bound = exact_and_bound(t.nonzero_masks, t.sign_masks, t.scales, x)
             assert_within(y, y64, bound, f"L{li}.{name}", slack=_half_ulp(y64))
+
+
+def test_group_packed_back_to_back_runs_as_one_matrix():
+    """prepare_group + the fused entry points: same results as one call per matrix, FP16 and INT8."""
+    from ternary_llm_b200 import layer_ops, synth
+    k = 2048
+    shapes = (1024, 256, 272)          # the last row count need not be a multiple of 16
+    mats = []
+    for i, n in enumerate(shapes):
+        nz, sg, sc = synth.random_ternary_weight(n, k, seed=70 + i, device="cuda")
+        mats.append((nz, sg, sc, n, k))
+    group = tl.prepare_group(mats)
+    assert all(group[i + 1].packed.data_ptr() == group[i].packed.data_ptr() + group[i].packed.numel() for i in range(2))
+    x = torch.randn(k, device="cuda").half()
+    ys = [torch.zeros(n, dtype=torch.float16, device="cuda") for n in shapes]
+    tl.ternary_gemv_packed_multi(group, x, ys)
+    for w, y in zip(group, ys):
+        y1 = torch.zeros_like(y)
+        tl.ternary_gemv_packed(w, x, y1, 1)
+        torch.cuda.synchronize()
+        # the split over CTAs differs between the two launches, hence the order of the FP32 partial sums
+        assert (y.float().cpu() - y1.float().cpu()).abs().max() <= 2.0 ** -10 * max(1.0, float(y1.float().abs().max()))
+    q = torch.zeros(k, dtype=torch.int8, device="cuda")
+    scale = torch.zeros(1, dtype=torch.float32, device="cuda")
+    tl.quantize_absmax_int8(x, q, scale, k)
+    yi = [torch.zeros(n, dtype=torch.float16, device="cuda") for n in shapes]
+    layer_ops.ternary_gemv_int8_packed_multi(group, q, scale, yi)
+    for w, y in zip(group, yi):
+        y1 = torch.zeros_like(y)
+        tl.ternary_gemv_int8_packed(w, q, float(scale.item()), y1)
+        torch.cuda.synchronize()
+        assert (y.float().cpu() - y1.float().cpu()).abs().max() <= 2.0 ** -10 * max(1.0, float(y1.float().abs().max()))
+    tl.check_device_errors()
