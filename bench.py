@@ -48,6 +48,8 @@ def gemv_bytes(n: int, k: int, b: int = 1) -> int:
 
 LAYER_BYTES = sum(gemv_bytes(n, k) for _, n, k in SHAPES_8B)
 STEP_BYTES = LAYER_BYTES * LAYERS_8B
+# DRAM traffic of one [gate|up] launch (28672 x 4096) from the ncu capture in profiles/
+ROOF_TRAFFIC = 31233024
 
 
 def measured_peak_hbm():
@@ -457,18 +459,16 @@ def run_ours(args):
         with torch.cuda.graph(graph, stream=stream):
             launch_step()
 
-        # roofline kernel: gate/up GEMV alone over the 64 distinct gate/up matrices
-        gi = [i for i, s in enumerate(SHAPES_8B) if s[0] in ("gate", "up")]
-        n_r, k_r = 14336, 4096
+        # roofline kernel: the dominant launch of the step, [gate|up] (28672 x 4096 as one matrix),
+        # alone over the 32 distinct gate|up groups
+        n_r, k_r = 2 * 14336, 4096
         rgraph = torch.cuda.CUDAGraph()
         xr = x_dev[:k_r]
-        yr = torch.zeros(n_r, dtype=torch.float16, device=dev)
+        yr = [torch.zeros(14336, dtype=torch.float16, device=dev) for _ in range(2)]
         with torch.cuda.graph(rgraph, stream=stream):
             for li in range(LAYERS_8B):
-                for mi in gi:
-                    nz, sg, sc = layers[li][mi]
-                    tl.ternary_gemv(nz, sg, sc, xr, yr, n_r, k_r)
-        roof_launches = LAYERS_8B * len(gi)
+                tl.ternary_gemv_packed_multi(prepared[li * 7 + 4:li * 7 + 6], xr, yr)
+        roof_launches = LAYERS_8B
 
         def barrier():
             torch.cuda.synchronize()
@@ -573,9 +573,9 @@ def run_ours(args):
                        "launch": "CUDA graph replay of the whole step; q|k|v and gate|up are packed back to back at load time and each group is streamed as one matrix in one launch (they share the input vector); o and down one launch each",
                        "parallelism": "independent replicas per GPU" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": 15628288, "peak_kind": peak_kind,
-                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in profiles/gemv_packed_14336x4096_b1.md",
-                         "kernel": "gemv 14336x4096 batch 1", "bytes_per_launch": rb,
+                         "frac": achieved / peak, "traffic": ROOF_TRAFFIC, "peak_kind": peak_kind,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in profiles/gemv_packed_28672x4096_b1.md",
+                         "kernel": "gemv [gate|up] 28672x4096 batch 1 (gemv_packed_kernel<0>)", "bytes_per_launch": rb,
                          "us_per_launch": ms_roof * 1e3,
                          "frac_of_nominal_8000": achieved / 8000.0},
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
@@ -658,6 +658,23 @@ def run_case(args):
                     tl.ternary_gemv_packed(w, x, y, 1)
                 else:
                     tl.ternary_gemv_int8_packed(w, xq, 0.01, y)
+    elif kind == "gemv_group":
+        # gemv_group:N1+N2[+N3]xK[:copies] -- matrices packed back to back, one launch per group
+        ns, k = dims.split("x")
+        ns, k = [int(v) for v in ns.split("+")], int(k)
+        copies = int(rest[0]) if rest else 6
+        groups = []
+        for c in range(copies):
+            mats = []
+            for i, n in enumerate(ns):
+                nz, sg, sc = synth.random_ternary_weight(n, k, seed=10 * c + i, device=dev)
+                mats.append((nz, sg, sc, n, k))
+            groups.append(tl.prepare_group(mats))
+        x = torch.randn(k, device=dev).half()
+        ys = [torch.zeros(n, device=dev, dtype=torch.float16) for n in ns]
+        for _ in range(2):
+            for g in groups:
+                tl.ternary_gemv_packed_multi(g, x, ys)
     elif kind == "gemm":
         m, n, k = (int(v) for v in dims.split("x"))
         nz, sg, sc = synth.random_ternary_weight(n, k, seed=0, device=dev)
@@ -723,7 +740,7 @@ def main():
                     help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
-                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]]")
+                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemv_group:N1+N2xK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]]")
     args = ap.parse_args()
     if args.case:
         return run_case(args)
