@@ -223,11 +223,16 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
     layers = []
     _log(rank, f"generating {n_layers} layers of tp{world} shards")
     for li in range(n_layers):
-        mats = []
+        src = []
         for mi, (_, n, k) in enumerate(shapes):
             nz, sg, sc = synth.random_ternary_weight(n, k, seed=1_000_000 * rank + 100 * li + mi, device=dev)
-            mats.append(tl.PreparedWeight(nz, sg, sc, n, k, register=False, keep_source=False))
-            del nz, sg, sc
+            src.append((nz, sg, sc, n, k))
+        # q|k|v and gate|up shards are packed back to back: one launch per group
+        mats = tl.prepare_group(src[0:3])
+        mats.append(tl.PreparedWeight(*src[3], register=False, keep_source=False))
+        mats += tl.prepare_group(src[4:6])
+        mats.append(tl.PreparedWeight(*src[6], register=False, keep_source=False))
+        del src
         layers.append(mats)
     gen = torch.Generator(device=dev).manual_seed(99)
     x_h = torch.randn(H70, generator=gen, device=dev).half()            # layer input (replicated)
