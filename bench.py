@@ -358,7 +358,8 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             "dtype": "s8 MMA (exact s32 group sums), f32 accumulate", "data": "synthetic",
             "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, %d layers), batch 1, decode-style pass" % n_layers,
                        "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, all-reduce of the 8192-vector after o and after down (160 per step): " + ("fused into the row-parallel GEMV kernel (peer stores over NVLink, flags, local sum)" if fused else "NCCL"),
-                       "gemv_per_step_per_gpu": launches, "bytes_per_step": step_bytes,
+                       "gemv_per_step_per_gpu": launches, "kernel_launches_per_step_per_gpu": 4 * n_layers + (0 if fused else 2 * n_layers),
+                       "bytes_per_step": step_bytes,
                        "l2": f"{per_gpu_bytes/1e9:.2f} GB of distinct weights per GPU per step (> 126 MB L2), no flush needed",
                        "launch": mode},
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
@@ -367,7 +368,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": 2 * H70 * world, "d2h_bytes_per_step": 2 * H70 * world,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches * args.steps, "clocks": clocks,
+            "gpu_launches": 4 * n_layers * args.steps, "clocks": clocks,
         }), flush=True)
     # Tearing down a process group whose collectives were captured in a CUDA graph can
     # block forever: drop the graph, drain the device, meet at a barrier, then leave
