@@ -64,12 +64,6 @@ int launch_gemv_int8_packed_quant(const uint8_t* packed, const half* x, half* y,
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream);
 
-// tcgen05 INT8 GEMV (gemv_tc5.cu): one FP16 vector (xq == nullptr) or one INT8 vector.
-// Returns TLLM_ERR_SIZE when the shape is not supported (the caller then uses gemv_mma.cu).
-bool gemv_tc5_supported(int rows, int cols);
-int launch_gemv_tc5(const uint8_t* packed, const half* x, const int8_t* xq, float in_scale, const float* in_scale_dev,
-                    half* y, int rows, int cols, int nseg, const int* seg_rows, half* const* seg_y, cudaStream_t stream);
-
 // tcgen05 prefill GEMM on prepared weights (gemm_tcgen05.cu).
 bool gemm_tcgen05_supported(int M, int N, int K);
 int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, int N, int K, cudaStream_t stream);

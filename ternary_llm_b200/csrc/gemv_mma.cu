@@ -33,7 +33,6 @@
 // and outputs written after it, so a GEMV's weight stream starts while the kernel
 // before it in the stream drains.  Every mbarrier wait is bounded; a wait that
 // gives up records TLLM_ERR_TIMEOUT in a device flag and the kernel returns.
-#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -1160,17 +1159,6 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     DeviceScratch* s = nullptr;
     int st = get_scratch(&s);
     if (st) return st;
-    // single vector, no fused staging: the tcgen05 kernel when it is switched on
-    static const int use_tc5 = [] {
-        const char* e = getenv("TLLM_GEMV_TC5");
-        return e ? atoi(e) : 0;
-    }();
-    if (use_tc5 && !fx && (mode == kF16B1 || mode == kI8)) {
-        st = launch_gemv_tc5(packed, mode == kI8 ? nullptr : (const half*)x, mode == kI8 ? (const int8_t*)x : nullptr,
-                             in_scale, in_scale_dev, y, rows, cols, seg ? seg->n : 0, seg ? seg->rows : nullptr,
-                             seg ? seg->y : nullptr, stream);
-        if (st != TLLM_ERR_SIZE) return st;
-    }
     GemvArgs a = {};
     a.packed = packed;
     a.x = x;
