@@ -308,6 +308,12 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     if (c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.n_heads % c.n_kv_heads || c.head_dim % 8 ||
         c.hidden_dim % kGroup || c.intermediate_dim % kGroup || (c.n_heads * c.head_dim) % kGroup || c.max_seq_len <= 0)
         return fail(TLLM_ERR_SHAPE, "decoder_create: unsupported configuration");
+    {
+        // what the attention kernels take: head_dim 16/32/64/128, at most 16 query heads per KV head
+        const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads;
+        if (!(hd == 16 || hd == 32 || hd == 64 || hd == 128) || group > 16 || group * (hd / 8) > 256)
+            return fail(TLLM_ERR_SHAPE, "decoder_create: head_dim=%d with %d query heads per KV head is not supported", hd, group);
+    }
     Decoder* D = new Decoder();
     D->d = c;
     D->flags = flags;
