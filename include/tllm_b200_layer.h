@@ -109,6 +109,7 @@ typedef struct tllm_b200_model_desc {
     const tllm_b200_layer_weights* layers; /* host array of n_layers */
 } tllm_b200_model_desc;
 
+#define TLLM_DECODER_MAX_BATCH 64
 #define TLLM_DECODER_INT8_DECODE 1 /* single-token steps quantise activations to INT8 (the reference's choice, src/transformer.cpp:182) */
 
 /* Transformer::Transformer, src/transformer.cpp:29-72: allocates the KV caches and the
@@ -118,6 +119,12 @@ typedef struct tllm_b200_model_desc {
 int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void** out);
 void tllm_b200_decoder_destroy(void* decoder);
 
+/* The same with room for max_batch (1..TLLM_DECODER_MAX_BATCH) independent sequences, each
+ * with its own KV cache.  The reference's Transformer serves one sequence
+ * (src/transformer.cpp:226-242 pass batch 1 to every operator although the operators take a
+ * batch); no counterpart there. */
+int tllm_b200_decoder_create_batched(const tllm_b200_model_desc* desc, int flags, int max_batch, void** out);
+
 /* Transformer::reset, src/transformer.cpp:91-97. */
 int tllm_b200_decoder_reset(void* decoder, void* stream);
 
@@ -126,6 +133,18 @@ int tllm_b200_decoder_reset(void* decoder, void* stream);
  * pointer to half [vocab] for the last token (owned by the decoder). */
 int tllm_b200_decoder_forward(void* decoder, const int* token_ids, int n_tokens, int start_pos, void** logits,
                               void* stream);
+
+/* forward for sequence `seq` (0..max_batch-1) of a batched decoder: its own KV cache, logits
+ * in its own row of the decoder's [max_batch, vocab] buffer. */
+int tllm_b200_decoder_forward_seq(void* decoder, int seq, const int* token_ids, int n_tokens, int start_pos,
+                                  void** logits, void* stream);
+
+/* One decode step of `batch` sequences in lock step: token_ids[b] is the next token of
+ * sequence b, all at cache position pos; the weights are read once for the whole batch (FP16
+ * activations: passes of the streaming GEMV up to 6 sequences, the tcgen05 GEMM above).
+ * *logits: half [batch, vocab]. */
+int tllm_b200_decoder_forward_batch(void* decoder, const int* token_ids, int batch, int pos, void** logits,
+                                    void* stream);
 
 /* The greedy decode loop of the reference's generate() (src/main.cpp:140-163, sampling
  * reduced to argmax) with nothing on the host inside it: one decode step -- forward of

@@ -49,7 +49,10 @@ SIGNATURES = {
     "tllm_b200_fp16_gemm": (_int, [_vp] * 3 + [_int] * 3 + [_vp]),
     "tllm_b200_gemv_int8_packed_multi": (_int, [_int, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "tllm_b200_decoder_create": (_int, [_vp, _int, _vp]),
+    "tllm_b200_decoder_create_batched": (_int, [_vp, _int, _int, _vp]),
     "tllm_b200_decoder_destroy": (None, [_vp]),
+    "tllm_b200_decoder_forward_seq": (_int, [_vp, _int, _vp, _int, _int, _vp, _vp]),
+    "tllm_b200_decoder_forward_batch": (_int, [_vp, _vp, _int, _int, _vp, _vp]),
     "tllm_b200_decoder_reset": (_int, [_vp, _vp]),
     "tllm_b200_decoder_forward": (_int, [_vp, _vp, _int, _int, _vp, _vp]),
     "tllm_b200_decoder_generate": (_int, [_vp, _int, _int, _int, _vp, _vp]),

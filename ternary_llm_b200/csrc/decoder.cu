@@ -49,6 +49,7 @@ struct Decoder {
     half *qkv1 = nullptr, *gu1 = nullptr;      // single-token outputs of the concatenated matrices
     half* residual2 = nullptr;                 // second residual vector of the fused single-token step
     bool fused_ok = false;                     // every layer has concatenated q|k|v and gate|up
+    int max_batch = 1;                         // sequences with their own KV cache
     int8_t* xq = nullptr;
     float* xscale = nullptr;
     float* attn_ws = nullptr;
@@ -165,13 +166,20 @@ int linear_multi(Decoder* D, int count, const PackedW* const* w, half* const* y,
     return TLLM_OK;
 }
 
-// One pass of the layer stack.  pos_dev != nullptr: single token whose position is read
-// from device memory (start_pos ignored).
-int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_dev, cudaStream_t s)
+// One pass of the layer stack.
+//   batch == 0: n tokens of sequence `seq` at positions start_pos.. (pos_dev != nullptr: one
+//               token whose position is read from device memory, start_pos ignored);
+//   batch  > 0: one token of each of the sequences 0..batch-1 (n == batch), all at position
+//               start_pos, each against its own KV cache; logits for every sequence.
+int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_dev, int seq, int batch, cudaStream_t s)
 {
     const tllm_b200_model_desc& c = D->d;
     const int hidden = c.hidden_dim, inter = c.intermediate_dim, qdim = c.n_heads * c.head_dim;
     const bool i8 = (n == 1) && (D->flags & TLLM_DECODER_INT8_DECODE);
+    const int bsz = batch > 0 ? batch : 1, seq_n = batch > 0 ? 1 : n;       // attention geometry
+    const size_t kv_seq = (size_t)c.max_seq_len * c.n_kv_heads * c.head_dim;  // one sequence's cache of a layer
+    const size_t kv_layer = kv_seq * D->max_batch;
+    const size_t kv_first = batch > 0 ? 0 : (size_t)seq * kv_seq;
     int8_t* xq = i8 ? D->xq : nullptr;
     float* xs = i8 ? D->xscale : nullptr;
     int st;
@@ -186,7 +194,7 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
         const size_t kvdim = (size_t)c.n_kv_heads * c.head_dim;
         for (int l = 0; l < c.n_layers; l++) {
             const LayerW& L = D->layers[l];
-            const size_t kv_off = (size_t)l * c.max_seq_len * kvdim;
+            const size_t kv_off = (size_t)l * kv_layer + kv_first;
             half *qb = D->qkv1, *kb = qb + qdim, *vb = kb + kvdim, *gb = D->gu1, *ub = gb + inter;
             if (l == 0) {
                 TRY(launch_gemv_int8_packed_norm(L.qkv.p, res_cur, nullptr, L.attn_norm, nullptr, c.rms_norm_eps, qb,
@@ -208,7 +216,7 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
     } else
     for (int l = 0; l < c.n_layers; l++) {
         const LayerW& L = D->layers[l];
-        const size_t kv_off = (size_t)l * c.max_seq_len * c.n_kv_heads * c.head_dim;
+        const size_t kv_off = (size_t)l * kv_layer + kv_first;
         // pre-attention norm; from the second layer on it also adds the previous FFN output
         if (l == 0)
             TRY(launch_rmsnorm(D->residual, L.attn_norm, D->hidden, nullptr, nullptr, xq, xs, n, hidden, c.rms_norm_eps, 0, s));
@@ -228,14 +236,14 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
             half* y[3] = {qb, kb, vb};
             TRY(linear_multi(D, 3, w, y, D->hidden, i8, n, s));
         }
-        TRY(launch_rope(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, 1, n, c.n_heads, c.n_kv_heads,
+        TRY(launch_rope(qb, kb, vb, D->k_cache + kv_off, D->v_cache + kv_off, bsz, seq_n, c.n_heads, c.n_kv_heads,
                         c.head_dim, start_pos, pos_dev, c.rope_theta, c.max_seq_len, 1, s));
         if (pos_dev)
             TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
                                  c.head_dim, 1, 1, c.max_seq_len, pos_dev, D->attn_ws, D->attn_counters, s));
         else
-            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, 1, c.n_heads, c.n_kv_heads,
-                                 c.head_dim, n, start_pos + n, c.max_seq_len, nullptr, D->attn_ws, D->attn_counters, s));
+            TRY(launch_attention(qb, D->k_cache + kv_off, D->v_cache + kv_off, D->attn_out, bsz, c.n_heads, c.n_kv_heads,
+                                 c.head_dim, seq_n, start_pos + seq_n, c.max_seq_len, nullptr, D->attn_ws, D->attn_counters, s));
         if (i8) TRY(launch_quantize_absmax_int8(D->attn_out, D->xq, D->xscale, qdim, s));
         {
             const PackedW* w[1] = {&L.o};
@@ -262,20 +270,29 @@ int forward(Decoder* D, const int* tokens, int n, int start_pos, const int* pos_
             TRY(linear_multi(D, 1, w, y, gb, i8, n, s));
         }
     }
+    const bool tern_head = (c.lm_head_weight == nullptr);
+    if (batch > 0) {
+        // last residual add + final norm + lm_head for every sequence
+        TRY(launch_rmsnorm(D->ffn_out, static_cast<const half*>(c.final_norm_weight), D->hidden, res_cur, res_cur, nullptr,
+                           nullptr, n, hidden, c.rms_norm_eps, 1, s));
+        if (tern_head) TRY(linear_f16(D->lm_head, D->hidden, D->logits, n, s));
+        else TRY(launch_fp16_gemv_batched(static_cast<const half*>(c.lm_head_weight), D->hidden, D->logits, n, c.vocab_size, hidden, s));
+        return TLLM_OK;
+    }
     // last residual add + final norm, last token only
     const size_t last = (size_t)(n - 1) * hidden;
-    const bool tern_head = (c.lm_head_weight == nullptr);
     const bool head_i8 = tern_head;     // a ternary lm_head always takes the INT8 path (src/transformer.cpp:308-311)
+    half* logits = D->logits + (size_t)seq * c.vocab_size;
     TRY(launch_rmsnorm(D->ffn_out + last, static_cast<const half*>(c.final_norm_weight), D->hidden, res_cur + last,
                        res_cur + last, head_i8 ? D->xq : nullptr, head_i8 ? D->xscale : nullptr, 1, hidden,
                        c.rms_norm_eps, 1, s));
     if (tern_head) {
         const uint8_t* p[1] = {D->lm_head.p};
-        half* y[1] = {D->logits};
+        half* y[1] = {logits};
         int rows[1] = {D->lm_head.rows};
         TRY(launch_gemv_int8_packed_multi(1, p, y, rows, D->lm_head.cols, D->xq, D->xscale, s));
     } else {
-        TRY(launch_fp16_gemv(static_cast<const half*>(c.lm_head_weight), D->hidden, D->logits, c.vocab_size, hidden, s));
+        TRY(launch_fp16_gemv(static_cast<const half*>(c.lm_head_weight), D->hidden, logits, c.vocab_size, hidden, s));
     }
 #undef TRY
     return TLLM_OK;
@@ -301,8 +318,15 @@ void tllm_b200_decoder_destroy(void* decoder)
 
 int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void** out)
 {
+    return tllm_b200_decoder_create_batched(desc, flags, 1, out);
+}
+
+int tllm_b200_decoder_create_batched(const tllm_b200_model_desc* desc, int flags, int max_batch, void** out)
+{
     if (!desc || !out || !desc->layers || !desc->embedding_table || !desc->final_norm_weight)
         return fail(TLLM_ERR_NULL, "decoder_create: null argument");
+    if (max_batch < 1 || max_batch > TLLM_DECODER_MAX_BATCH)
+        return fail(TLLM_ERR_BATCH, "decoder_create: max_batch=%d outside 1..%d", max_batch, TLLM_DECODER_MAX_BATCH);
     const tllm_b200_model_desc& c = *desc;
     if (c.group_size != kGroup) return fail(TLLM_ERR_GROUP, "decoder_create: group_size=%d (must be 128)", c.group_size);
     if (c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.n_heads % c.n_kv_heads || c.head_dim % 8 ||
@@ -317,6 +341,7 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     Decoder* D = new Decoder();
     D->d = c;
     D->flags = flags;
+    D->max_batch = max_batch;
     int st = TLLM_OK;
     auto bail = [&](int code) {
         tllm_b200_decoder_destroy(D);
@@ -348,11 +373,11 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     D->d.layers = nullptr;      // the caller's array is not referenced after this call
     if (!c.lm_head_weight && (st = pack(D, c.lm_head_ternary, &D->lm_head, D->stream))) return bail(st);
 
-    const size_t mt = (size_t)c.max_seq_len;
+    const size_t mt = (size_t)(c.max_seq_len > max_batch ? c.max_seq_len : max_batch);   // activation rows
     const size_t qdim = (size_t)c.n_heads * c.head_dim, kvdim = (size_t)c.n_kv_heads * c.head_dim;
     size_t maxdim = (size_t)c.hidden_dim > (size_t)c.intermediate_dim ? c.hidden_dim : c.intermediate_dim;
     if (qdim > maxdim) maxdim = qdim;
-    const size_t kv_elems = (size_t)c.n_layers * mt * kvdim;
+    const size_t kv_elems = (size_t)c.n_layers * max_batch * c.max_seq_len * kvdim;
 #define ALLOC(x) do { if ((st = (x)) != TLLM_OK) return bail(st); } while (0)
     ALLOC(dev_alloc(D, &D->residual, mt * c.hidden_dim, true));
     ALLOC(dev_alloc(D, &D->hidden, mt * c.hidden_dim, true));
@@ -364,7 +389,7 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     ALLOC(dev_alloc(D, &D->gate, mt * c.intermediate_dim, true));
     ALLOC(dev_alloc(D, &D->up, mt * c.intermediate_dim, true));
     ALLOC(dev_alloc(D, &D->ffn_out, mt * c.hidden_dim, true));
-    ALLOC(dev_alloc(D, &D->logits, (size_t)c.vocab_size, true));
+    ALLOC(dev_alloc(D, &D->logits, (size_t)max_batch * c.vocab_size, true));
     ALLOC(dev_alloc(D, &D->k_cache, kv_elems, true));
     ALLOC(dev_alloc(D, &D->v_cache, kv_elems, true));
     ALLOC(dev_alloc(D, &D->residual2, (size_t)c.hidden_dim, true));
@@ -372,9 +397,9 @@ int tllm_b200_decoder_create(const tllm_b200_model_desc* desc, int flags, void**
     ALLOC(dev_alloc(D, &D->gu1, (size_t)2 * c.intermediate_dim, true));
     ALLOC(dev_alloc(D, &D->xq, maxdim, true));
     ALLOC(dev_alloc(D, &D->xscale, 4, true));
-    ALLOC(dev_alloc(D, &D->attn_ws, attention_workspace_bytes(1, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));
+    ALLOC(dev_alloc(D, &D->attn_ws, attention_workspace_bytes(max_batch, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));
     ALLOC(dev_alloc(D, &D->attn_ws2, attention_decode_workspace_bytes(c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq_len) / sizeof(float), true));
-    ALLOC(dev_alloc(D, &D->attn_counters, (size_t)c.n_kv_heads, true));
+    ALLOC(dev_alloc(D, &D->attn_counters, (size_t)max_batch * c.n_kv_heads, true));
     ALLOC(dev_alloc(D, &D->state, 4, true));
     D->history_cap = c.max_seq_len;
     ALLOC(dev_alloc(D, &D->history, (size_t)D->history_cap, true));
@@ -392,7 +417,7 @@ int tllm_b200_decoder_reset(void* decoder, void* stream)
 {
     Decoder* D = static_cast<Decoder*>(decoder);
     if (!D) return fail(TLLM_ERR_NULL, "decoder_reset: null decoder");
-    const size_t bytes = (size_t)D->d.n_layers * D->d.max_seq_len * D->d.n_kv_heads * D->d.head_dim * sizeof(half);
+    const size_t bytes = (size_t)D->d.n_layers * D->max_batch * D->d.max_seq_len * D->d.n_kv_heads * D->d.head_dim * sizeof(half);
     cudaMemsetAsync(D->k_cache, 0, bytes, static_cast<cudaStream_t>(stream));
     cudaMemsetAsync(D->v_cache, 0, bytes, static_cast<cudaStream_t>(stream));
     return check_launch("decoder_reset");
@@ -401,12 +426,31 @@ int tllm_b200_decoder_reset(void* decoder, void* stream)
 int tllm_b200_decoder_forward(void* decoder, const int* token_ids, int n_tokens, int start_pos, void** logits,
                               void* stream)
 {
+    return tllm_b200_decoder_forward_seq(decoder, 0, token_ids, n_tokens, start_pos, logits, stream);
+}
+
+int tllm_b200_decoder_forward_seq(void* decoder, int seq, const int* token_ids, int n_tokens, int start_pos,
+                                  void** logits, void* stream)
+{
     Decoder* D = static_cast<Decoder*>(decoder);
     if (!D || !token_ids || !logits) return fail(TLLM_ERR_NULL, "decoder_forward: null argument");
+    if (seq < 0 || seq >= D->max_batch) return fail(TLLM_ERR_BATCH, "decoder_forward: sequence %d outside 0..%d", seq, D->max_batch - 1);
     if (n_tokens < 1 || start_pos < 0 || start_pos + n_tokens > D->d.max_seq_len)
         return fail(TLLM_ERR_SHAPE, "decoder_forward: n_tokens=%d start_pos=%d max_seq_len=%d", n_tokens, start_pos,
                     D->d.max_seq_len);
-    const int st = forward(D, token_ids, n_tokens, start_pos, nullptr, static_cast<cudaStream_t>(stream));
+    const int st = forward(D, token_ids, n_tokens, start_pos, nullptr, seq, 0, static_cast<cudaStream_t>(stream));
+    if (st) return st;
+    *logits = D->logits + (size_t)seq * D->d.vocab_size;
+    return TLLM_OK;
+}
+
+int tllm_b200_decoder_forward_batch(void* decoder, const int* token_ids, int batch, int pos, void** logits, void* stream)
+{
+    Decoder* D = static_cast<Decoder*>(decoder);
+    if (!D || !token_ids || !logits) return fail(TLLM_ERR_NULL, "decoder_forward_batch: null argument");
+    if (batch < 1 || batch > D->max_batch) return fail(TLLM_ERR_BATCH, "decoder_forward_batch: batch=%d outside 1..%d", batch, D->max_batch);
+    if (pos < 0 || pos >= D->d.max_seq_len) return fail(TLLM_ERR_SHAPE, "decoder_forward_batch: pos=%d max_seq_len=%d", pos, D->d.max_seq_len);
+    const int st = forward(D, token_ids, batch, pos, nullptr, 0, batch, static_cast<cudaStream_t>(stream));
     if (st) return st;
     *logits = D->logits;
     return TLLM_OK;
@@ -427,7 +471,7 @@ int tllm_b200_decoder_generate(void* decoder, int first_token, int start_pos, in
     const int init[3] = {first_token, start_pos, 0};
     cudaMemcpyAsync(D->state, init, sizeof(init), cudaMemcpyHostToDevice, s);
     auto step = [&]() -> int {
-        int e = forward(D, D->state, 1, 0, D->state + 1, s);
+        int e = forward(D, D->state, 1, 0, D->state + 1, 0, 0, s);
         if (e) return e;
         if ((e = launch_argmax(D->logits, D->d.vocab_size, D->state, D->history, D->state + 2, D->am_val, D->am_idx,
                                D->am_counter, s)))

@@ -21,6 +21,8 @@ int launch_silu_mul(const half* gate, const half* up, half* out, long long size,
 int launch_add(const half* a, const half* b, half* out, long long size, cudaStream_t stream);
 int launch_embedding(const half* table, const int* indices, half* out, int n_tokens, int dim, cudaStream_t stream);
 int launch_fp16_gemv(const half* w, const half* x, half* y, int rows, int cols, cudaStream_t stream);
+// y[b, r] = W[r, :] . x[b, :] for `batch` vectors (x [batch, cols], y [batch, rows]).
+int launch_fp16_gemv_batched(const half* w, const half* x, half* y, int batch, int rows, int cols, cudaStream_t stream);
 int launch_fp16_gemm(const half* A, const half* B, half* C, int M, int N, int K, cudaStream_t stream);
 // part_val / part_idx: 64 entries each; counter: one zero-initialised unsigned.
 int launch_argmax(const half* logits, int n, int* out, int* history, int* step, float* part_val, int* part_idx,

@@ -470,6 +470,90 @@ int launch_fp16_gemv(const half* w, const half* x, half* y, int rows, int cols, 
                       y, rows, cols);
 }
 
+// Several vectors at once (batched decode): y[b, r] = W[r, :] . x[b, :].  The vectors are taken
+// eight at a time: staged in shared memory, every weight row read once per eight vectors.
+constexpr int kFp16GemvVecs = 8;
+
+__global__ void __launch_bounds__(kFp16GemvWarps * 32)
+fp16_gemv_batched_kernel(const half* __restrict__ w, const half* __restrict__ x, half* __restrict__ y, int batch,
+                         int rows, int cols)
+{
+    extern __shared__ __align__(16) half xs[];          // [kFp16GemvVecs][cols]
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();
+    for (int b0 = 0; b0 < batch; b0 += kFp16GemvVecs) {
+        const int nb = min(kFp16GemvVecs, batch - b0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) xs[i] = x[(size_t)b0 * cols + i];
+        __syncthreads();
+        for (int r = blockIdx.x * kFp16GemvWarps + warp; r < rows; r += gridDim.x * kFp16GemvWarps) {
+            const half* wr = w + (size_t)r * cols;
+            float acc[kFp16GemvVecs];
+#pragma unroll
+            for (int b = 0; b < kFp16GemvVecs; b++) acc[b] = 0.f;
+            if ((cols & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+                for (int c = lane; c < (cols >> 3); c += 32) {
+                    const uint4 a = __ldcs(reinterpret_cast<const uint4*>(wr) + c);
+                    const half2* ah = reinterpret_cast<const half2*>(&a);
+                    float2 fa[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) fa[j] = __half22float2(ah[j]);
+#pragma unroll
+                    for (int b = 0; b < kFp16GemvVecs; b++) {
+                        if (b < nb) {
+                            const uint4 xv = *(reinterpret_cast<const uint4*>(xs + (size_t)b * cols) + c);
+                            const half2* xh = reinterpret_cast<const half2*>(&xv);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float2 fx = __half22float2(xh[j]);
+                                acc[b] = fmaf(fa[j].x, fx.x, acc[b]);
+                                acc[b] = fmaf(fa[j].y, fx.y, acc[b]);
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int c = lane; c < cols; c += 32) {
+                    const float fw = __half2float(wr[c]);
+#pragma unroll
+                    for (int b = 0; b < kFp16GemvVecs; b++)
+                        if (b < nb) acc[b] = fmaf(fw, __half2float(xs[(size_t)b * cols + c]), acc[b]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < kFp16GemvVecs; b++) {
+                if (b < nb) {
+                    const float v = warp_sum(acc[b]);
+                    if (lane == 0) y[(size_t)(b0 + b) * rows + r] = __float2half_rn(v);
+                }
+            }
+        }
+    }
+}
+
+int launch_fp16_gemv_batched(const half* w, const half* x, half* y, int batch, int rows, int cols, cudaStream_t stream)
+{
+    if (rows == 0 || batch == 0) return TLLM_OK;
+    if (batch == 1) return launch_fp16_gemv(w, x, y, rows, cols, stream);
+    const size_t smem = (size_t)kFp16GemvVecs * cols * sizeof(half);
+    if (smem > 200 * 1024) return fail(TLLM_ERR_SHAPE, "fp16_gemv (batched): cols=%d exceeds %d", cols, 200 * 1024 / 16);
+    static bool attr[64] = {};
+    static int sms[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr[dev]) {
+        cudaFuncSetAttribute(fp16_gemv_batched_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        attr[dev] = true;
+    }
+    long long grid = ((long long)rows + kFp16GemvWarps - 1) / kFp16GemvWarps;
+    const long long cap = (long long)sms[dev] * 4;
+    if (grid > cap) grid = cap;
+    return launch_pdl("fp16_gemv_batched", fp16_gemv_batched_kernel, dim3((unsigned)grid), dim3(kFp16GemvWarps * 32), smem,
+                      stream, w, x, y, batch, rows, cols);
+}
+
 // ---------------------------------------------------------------------------
 // FP16 GEMM   C[M, N] = A[M, K] . B[N, K]^T, FP32 accumulation   reference: kernels/elementwise.cu:216-304
 // ---------------------------------------------------------------------------

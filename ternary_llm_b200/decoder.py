@@ -23,7 +23,9 @@ class _DevArray:
 
 
 class Decoder:
-    def __init__(self, model, device=None, int8_decode: bool = True):
+    def __init__(self, model, device=None, int8_decode: bool = True, max_batch: int = 1):
+        """max_batch > 1: room for that many independent sequences, each with its own KV cache
+        (forward_seq for one of them, forward_batch for a lock-step decode of several)."""
         if isinstance(model, str):
             model = read_tllm(model)
         assert isinstance(model, TllmFile)
@@ -67,23 +69,44 @@ class Decoder:
         handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
-            _lib.check(_lib.lib().tllm_b200_decoder_create(ctypes.byref(d), 1 if int8_decode else 0,
-                                                           ctypes.byref(handle)))
+            _lib.check(_lib.lib().tllm_b200_decoder_create_batched(ctypes.byref(d), 1 if int8_decode else 0,
+                                                                   max_batch, ctypes.byref(handle)))
         self._h = handle
+        self.max_batch = max_batch
         del staging
 
     def reset(self) -> None:
         _lib.check(_lib.lib().tllm_b200_decoder_reset(self._h, torch.cuda.current_stream().cuda_stream))
 
+    @staticmethod
+    def _check_tokens(token_ids):
+        if not (token_ids.is_cuda and token_ids.dtype == torch.int32 and token_ids.is_contiguous()):
+            raise TypeError("token_ids must be a contiguous int32 CUDA tensor")
+
     def forward(self, token_ids, start_pos: int) -> torch.Tensor:
         """token_ids: int32 CUDA tensor [n]; returns the FP16 logits of the last token
         (a view of the decoder's buffer, overwritten by the next call)."""
-        if not (token_ids.is_cuda and token_ids.dtype == torch.int32 and token_ids.is_contiguous()):
-            raise TypeError("token_ids must be a contiguous int32 CUDA tensor")
+        return self.forward_seq(0, token_ids, start_pos)
+
+    def forward_seq(self, seq: int, token_ids, start_pos: int) -> torch.Tensor:
+        """forward for sequence `seq` of a batched decoder (its own KV cache)."""
+        self._check_tokens(token_ids)
         out = ctypes.c_void_p()
-        _lib.check(_lib.lib().tllm_b200_decoder_forward(self._h, token_ids.data_ptr(), token_ids.numel(), start_pos,
-                                                        ctypes.byref(out), torch.cuda.current_stream().cuda_stream))
+        _lib.check(_lib.lib().tllm_b200_decoder_forward_seq(self._h, seq, token_ids.data_ptr(), token_ids.numel(),
+                                                            start_pos, ctypes.byref(out),
+                                                            torch.cuda.current_stream().cuda_stream))
         return torch.as_tensor(_DevArray(out.value, self.config.vocab_size, "<f2"), device=self.device)
+
+    def forward_batch(self, token_ids, pos: int) -> torch.Tensor:
+        """One lock-step decode step: token_ids[b] is the next token of sequence b, all at cache
+        position pos.  Returns FP16 logits [batch, vocab] (a view of the decoder's buffer)."""
+        self._check_tokens(token_ids)
+        b = token_ids.numel()
+        out = ctypes.c_void_p()
+        _lib.check(_lib.lib().tllm_b200_decoder_forward_batch(self._h, token_ids.data_ptr(), b, pos, ctypes.byref(out),
+                                                              torch.cuda.current_stream().cuda_stream))
+        flat = torch.as_tensor(_DevArray(out.value, b * self.config.vocab_size, "<f2"), device=self.device)
+        return flat.view(b, self.config.vocab_size)
 
     def generate(self, first_token: int, start_pos: int, n_steps: int):
         """Greedy continuation: returns (tokens [n_steps], ms per step measured on the device)."""

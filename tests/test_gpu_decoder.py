@@ -53,6 +53,55 @@ def test_prefill_and_decode_logits_against_the_oracle(ternary_head):
         dec.close()
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 1, 128), (4, 4, 64), (16, 1, 32), (8, 2, 16)])
+def test_fused_decode_attention_geometries(heads, kv_heads, head_dim):
+    """Single-token steps (RoPE + append + attention in one launch) for grouped-query, multi-head and
+    multi-query layouts, across the 128-position split boundary, against the oracle."""
+    hidden = max(256, heads * head_dim)
+    cfg = cfg_small(hidden_dim=hidden, intermediate_dim=512, n_layers=1, n_heads=heads, n_kv_heads=kv_heads,
+                    head_dim=head_dim, max_seq_len=192, vocab_size=512)
+    model = tf.random_model(cfg, seed=heads * 7 + head_dim)
+    t = toks(140, cfg.vocab_size, seed=2)
+    dec = tl.Decoder(model, int8_decode=True)
+    ora = LO.Transformer(model, int8_decode=True)
+    dec.forward(torch.from_numpy(t[:126]).cuda(), 0)
+    ora.forward(list(t[:126]), 0)
+    for i in range(126, 131):          # positions 126..130: one split, then two
+        got = dec.forward(torch.from_numpy(t[i:i + 1]).cuda(), i).float().cpu().numpy()
+        want = ora.forward([int(t[i])], i)
+        assert np.isfinite(got).all()
+        assert close(got, want, 4e-2), f"position {i}"
+    tl.check_device_errors()
+    dec.close()
+
+
+@pytest.mark.parametrize("batch", [2, 5, 9])
+def test_batched_lock_step_decode_matches_independent_sequences(batch):
+    """B sequences with their own KV caches decoded in lock step (GEMV passes up to 6 sequences,
+    the tcgen05 GEMM above) against the oracle run once per sequence (FP16 activations)."""
+    cfg = cfg_small(max_seq_len=64)
+    model = tf.random_model(cfg, seed=21)
+    dec = tl.Decoder(model, int8_decode=True, max_batch=batch)
+    oracles = [LO.Transformer(model, int8_decode=False) for _ in range(batch)]
+    prompts = [toks(7, cfg.vocab_size, seed=100 + b) for b in range(batch)]
+    for b in range(batch):
+        got = dec.forward_seq(b, torch.from_numpy(prompts[b]).cuda(), 0).float().cpu().numpy()
+        want = oracles[b].forward(list(prompts[b]), 0)
+        assert close(got, want, 2e-2), f"prefill of sequence {b}"
+    nxt = toks(batch, cfg.vocab_size, seed=7)
+    for step in range(3):
+        got = dec.forward_batch(torch.from_numpy(nxt).cuda(), 7 + step).float().cpu().numpy()
+        assert got.shape == (batch, cfg.vocab_size) and np.isfinite(got).all()
+        for b in range(batch):
+            want = oracles[b].forward([int(nxt[b])], 7 + step)
+            assert close(got[b], want, 4e-2), f"step {step} sequence {b}"
+        nxt = got.argmax(axis=1).astype(np.int32)
+    with pytest.raises(tl.TllmError):
+        dec.forward_seq(batch, torch.from_numpy(prompts[0]).cuda(), 0)
+    tl.check_device_errors()
+    dec.close()
+
+
 def test_generate_replays_the_same_steps_as_forward():
     cfg = cfg_small(n_layers=3, max_seq_len=320)
     model = tf.random_model(cfg, seed=3)
