@@ -705,6 +705,45 @@ def run_case(args):
         c = torch.zeros(m, n, device=dev, dtype=torch.float16)
         for _ in range(4):
             tl.ternary_gemm_packed(a, w, c, m)
+    elif kind == "decode_batch":
+        # decode_batch:1b|1b-4l:B[:prompt[:steps]] -- B sequences decoded in lock step (graph-replayed step)
+        from ternary_llm_b200 import tllm_format as tf
+        arch = dict(DECODE_ARCH_1B)
+        if dims == "1b-4l":
+            arch.update(n_layers=4, vocab_size=32000)
+        bsz = int(rest[0]) if rest else 8
+        n_prompt = int(rest[1]) if len(rest) > 1 else 512
+        n_steps = int(rest[2]) if len(rest) > 2 else 32
+        cfg = tf.TllmConfig(**arch)
+        dec = tl.Decoder(tf.random_model(cfg, seed=2026), int8_decode=True, max_batch=bsz)
+        rng = np.random.default_rng(0)
+        for b in range(bsz):
+            dec.forward_seq(b, torch.from_numpy(rng.integers(0, cfg.vocab_size, n_prompt).astype(np.int32)).to(dev), 0)
+        toks = torch.from_numpy(rng.integers(0, cfg.vocab_size, bsz).astype(np.int32)).to(dev)
+        dec.forward_batch(toks, n_prompt)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            graphs = []
+            for i in range(n_steps):            # one graph per position (the position is a launch argument here)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    dec.forward_batch(toks, n_prompt + i)
+                graphs.append(g)
+            for g in graphs[:3]:
+                g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for g in graphs:
+                g.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n_steps
+        tl.check_device_errors()
+        print(json.dumps({"case": args.case, "status": "ok", "batch": bsz, "ms_per_step": ms,
+                          "tok_per_s_all_sequences": bsz * 1e3 / ms}))
+        return
     elif kind == "decode":
         # decode:ARCH[:prompt[:steps[:eager]]] -- the library's decoder on a seeded random model of
         # the benchmark's 1B architecture (`1b`, 16 layers) or a 4-layer cut of it (`1b-4l`)
@@ -762,7 +801,7 @@ def main():
                     help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
-                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemv_group:N1+N2xK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]]")
+                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemv_group:N1+N2xK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]] | decode_batch:1b|1b-4l:B[:prompt[:steps]]")
     args = ap.parse_args()
     if args.case:
         return run_case(args)
