@@ -25,6 +25,8 @@
 // and every role falls through to the common exit, where TMEM is released.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "packed_layout.cuh"
 
@@ -66,6 +68,10 @@ struct Args {
     int M, N, K, groups;       // groups = K / 128
     int nrb;                   // ceil(N / 16)
     int* err;
+    // split-K (gridDim.z > 1): CTA z contracts stages [z*groups/ks, (z+1)*groups/ks) and writes an
+    // FP32 partial tile; the CTA of a tile that arrives last adds the partials in z order.
+    float* ws;                 // [tile][z][tokens of the tile][128] FP32
+    unsigned* counters;        // [tiles], zero between launches
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -190,11 +196,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
     __shared__ __align__(8) uint64_t bars[2 * kBStages + 2 * kAStages + 1];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ int last_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * kTileN;          // first output feature of the tile
     const int m0 = blockIdx.y * kTileM;          // first token of the tile
-    const int nstages = a.groups;                // one scale group per stage
+    const int ks = gridDim.z;
+    const int it0 = (int)(((long long)blockIdx.z * a.groups) / ks);          // first scale group of this CTA
+    const int nstages = (int)(((long long)(blockIdx.z + 1) * a.groups) / ks) - it0;   // one scale group per stage
 
     const uint32_t bar0 = smem_u32(bars);
     auto full_b = [&](int s) { return bar0 + 8u * s; };
@@ -236,8 +245,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
                 if (!mbar_wait(empty_b(s), ((it / kBStages) & 1) ^ 1, abortp)) { abort_flag = 1; break; }
                 mbar_expect_tx(full_b(s), kStageBytes);
                 const uint32_t dst = smem_u32(smem + (size_t)s * kStageBytes);
-                tma_load_2d(dst, &map_a, it * kStageK, m0, full_b(s));
-                tma_load_2d(dst + kBoxBytes, &map_a, it * kStageK + kBoxK, m0, full_b(s));
+                tma_load_2d(dst, &map_a, (it0 + it) * kStageK, m0, full_b(s));
+                tma_load_2d(dst + kBoxBytes, &map_a, (it0 + it) * kStageK + kBoxK, m0, full_b(s));
             }
         }
     } else if (warp == 1) {
@@ -268,7 +277,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
         const int n = n0 + row;
         const int rb = n >> 4, r16 = n & 15;
         const bool row_valid = rb < a.nrb;               // rows past the matrix expand to zeros
-        const uint8_t* tile0 = a.packed + (size_t)(row_valid ? rb : 0) * a.groups * kTileBytes;
+        const uint8_t* tile0 = a.packed + ((size_t)(row_valid ? rb : 0) * a.groups + it0) * kTileBytes;
         const int spos = (r16 < 8) ? 2 * r16 : 2 * (r16 - 8) + 1;
         const uint32_t lane_base = tmem + ((uint32_t)(row & ~31) << 16);   // this warp's 32 TMEM lanes
 
@@ -314,29 +323,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
         if (!ok) abort_flag = 1;
 
         // ---------------- epilogue: accumulator -> C ----------------
-        if (ok && mbar_wait(acc_full, 0, abortp)) {
+        const bool good = ok && mbar_wait(acc_full, 0, abortp);
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        if (good) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* wtile = a.ws + ((size_t)tile_id * ks + blockIdx.z) * kTileM * kTileN;
 #pragma unroll 1
             for (int cchunk = 0; cchunk < kTileM / 32; cchunk++) {
                 if (m0 + cchunk * 32 >= a.M) break;       // uniform: no tokens left in this chunk
                 uint32_t v[32];
                 tmem_ld32(lane_base + cchunk * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < a.N) {
+                if (ks == 1) {
+                    if (n < a.N) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + cchunk * 32 + j;
-                        if (m < a.M) a.C[(size_t)m * a.N + n] = __float2half_rn(__uint_as_float(v[j]));
+                        for (int j = 0; j < 32; j++) {
+                            const int m = m0 + cchunk * 32 + j;
+                            if (m < a.M) a.C[(size_t)m * a.N + n] = __float2half_rn(__uint_as_float(v[j]));
+                        }
                     }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (m0 + cchunk * 32 + j < a.M) wtile[(size_t)(cchunk * 32 + j) * kTileN + row] = __uint_as_float(v[j]);
                 }
             }
         } else {
             abort_flag = 1;
         }
+        if (ks > 1) {
+            // publish, count, and let the last CTA of the tile add the partials in z order (all 128
+            // epilogue threads take part in the two barriers whether or not their wait succeeded)
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (row == 0) {
+                const unsigned prev = atomicAdd(a.counters + tile_id, 1u);
+                last_flag = (prev == (unsigned)ks - 1u) ? 1 : 0;
+                if (last_flag) a.counters[tile_id] = 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (ks > 1 && last_flag && !abort_flag) {
+        // The tile's last CTA adds the partial tiles in z order, all eight warps: lane l sums
+        // features 4l..4l+3 (one 16-byte load per partial), warps take tokens round-robin, eight
+        // tokens per trip so that 8 * ks loads are in flight per thread.
+        __threadfence();
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        const int f4 = lane * 4;
+        const float* base = a.ws + (size_t)tile_id * ks * kTileM * kTileN + f4;
+        const int mt = min(kTileM, a.M - m0);
+        for (int mb = warp * 8; mb < mt; mb += 8 * (kThreads / 32)) {
+            float4 tot[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) tot[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int z = 0; z < ks; z++) {
+                float4 p[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    p[u] = (mb + u < mt) ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)z * kTileM + mb + u) * kTileN))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    tot[u].x += p[u].x;
+                    tot[u].y += p[u].y;
+                    tot[u].z += p[u].z;
+                    tot[u].w += p[u].w;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (mb + u >= mt) continue;
+                half* cp = a.C + (size_t)(m0 + mb + u) * a.N + n0 + f4;
+                const float v[4] = {tot[u].x, tot[u].y, tot[u].z, tot[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (n0 + f4 + j < a.N) cp[j] = __float2half_rn(v[j]);
+            }
+        }
+    }
     if (abort_flag && tid == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -372,10 +440,28 @@ bool gemm_tcgen05_supported(int M, int N, int K)
     return M >= 1 && K >= gemm::kStageK && K % gemm::kStageK == 0;
 }
 
+// Scratch of the split-K path: 4 regions handed out round-robin, so that launches on up to four
+// streams do not share one (launches on one stream are ordered).
+namespace gemm {
+constexpr size_t kSplitWsBytes = (size_t)24 << 20;
+constexpr int kSplitTickets = 4;
+constexpr int kSplitMaxTiles = 4096;
+struct SplitScratch {
+    float* ws = nullptr;
+    unsigned* counters = nullptr;
+    int sms = 0;
+    unsigned ticket = 0;
+    bool ready = false, failed = false;
+};
+static SplitScratch g_split[64];
+static std::mutex g_split_mu;
+}  // namespace gemm
+
 template <int TM>
-static int launch_tm(gemm::EncodeTiledFn enc, const half* A, const gemm::Args& a, cudaStream_t stream)
+static int launch_tm(gemm::EncodeTiledFn enc, const half* A, const gemm::Args& a_in, cudaStream_t stream)
 {
     using namespace gemm;
+    Args a = a_in;
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t strides[1] = {(cuuint64_t)a.K * sizeof(half)};
@@ -393,7 +479,36 @@ static int launch_tm(gemm::EncodeTiledFn enc, const half* A, const gemm::Args& a
         cudaFuncSetAttribute(gemm_kernel<TM>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr[dev] = true;
     }
-    const dim3 grid((a.N + kTileN - 1) / kTileN, (a.M + TM - 1) / TM);
+    dim3 grid((a.N + kTileN - 1) / kTileN, (a.M + TM - 1) / TM, 1);
+    // Too few tiles for the SMs: split K (at most four ways).
+    if (dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lk(g_split_mu);
+        SplitScratch& sc = g_split[dev];
+        if (!sc.sms) cudaDeviceGetAttribute(&sc.sms, cudaDevAttrMultiProcessorCount, dev);
+        const int tiles = (int)(grid.x * grid.y), slots = sc.sms * Cfg<TM>::kCtasPerSm;
+        int ks = 1;
+        if (tiles * 2 <= slots) ks = slots / tiles;
+        if (ks > a.groups / 8) ks = a.groups / 8;        // at least eight scale groups per split
+        if (ks > 4) ks = 4;
+        if (ks > 1 && tiles <= kSplitMaxTiles && (size_t)tiles * ks * TM * kTileN * sizeof(float) <= kSplitWsBytes && !sc.failed) {
+            if (!sc.ready) {
+                if (cudaMalloc(&sc.ws, kSplitWsBytes * kSplitTickets) != cudaSuccess ||
+                    cudaMalloc(&sc.counters, sizeof(unsigned) * kSplitMaxTiles * kSplitTickets) != cudaSuccess) {
+                    cudaGetLastError();
+                    sc.failed = true;
+                } else {
+                    cudaMemset(sc.counters, 0, sizeof(unsigned) * kSplitMaxTiles * kSplitTickets);
+                    sc.ready = true;
+                }
+            }
+            if (sc.ready) {
+                const unsigned t = sc.ticket++ % kSplitTickets;
+                a.ws = sc.ws + (size_t)t * (kSplitWsBytes / sizeof(float));
+                a.counters = sc.counters + (size_t)t * kSplitMaxTiles;
+                grid.z = ks;
+            }
+        }
+    }
     gemm_kernel<TM><<<grid, kThreads, Cfg<TM>::kSmem, stream>>>(map, a);
     return check_launch("gemm_tcgen05");
 }
@@ -415,6 +530,8 @@ int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, in
     a.groups = K / kStageK;
     a.nrb = (N + 15) / 16;
     a.err = err;
+    a.ws = nullptr;
+    a.counters = nullptr;
     // token tile: the smallest that holds M, 256 for long prefills
     if (M <= 32) return launch_tm<32>(enc, A, a, stream);
     if (M <= 64) return launch_tm<64>(enc, A, a, stream);
