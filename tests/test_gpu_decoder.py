@@ -130,6 +130,59 @@ def test_generate_replays_the_same_steps_as_forward():
     dec.close()
 
 
+def test_benchmark_shapes_properties():
+    """At the benchmark's 1B layer shapes (hidden 2048, 32/8 heads of 64, intermediate 8192; 2 layers,
+    a 4096-token vocabulary to keep it quick): the graph-replayed loop reproduces step-by-step
+    forward calls token for token, a repeated step is idempotent, and reset + prefill restores
+    the same logits bit for bit."""
+    cfg = tf.TllmConfig(vocab_size=4096, hidden_dim=2048, intermediate_dim=8192, n_layers=2, n_heads=32, n_kv_heads=8,
+                        head_dim=64, max_seq_len=512, rope_theta=500000.0, rms_norm_eps=1e-5)
+    model = tf.random_model(cfg, seed=4)
+    dec = tl.Decoder(model, int8_decode=True)
+    prompt = torch.from_numpy(toks(300, cfg.vocab_size, 3)).cuda()
+    l0 = dec.forward(prompt, 0).clone()
+    first = int(l0.float().argmax().item())
+    a = dec.forward(torch.tensor([first], dtype=torch.int32, device="cuda"), 300).clone()
+    b = dec.forward(torch.tensor([first], dtype=torch.int32, device="cuda"), 300).clone()
+    assert torch.equal(a, b), "a repeated step must rewrite the same cache slot and logits"
+    want, tok, pos = [], first, 300
+    for _ in range(10):
+        tok = int(dec.forward(torch.tensor([tok], dtype=torch.int32, device="cuda"), pos).float().argmax().item())
+        want.append(tok)
+        pos += 1
+    dec.reset()
+    l1 = dec.forward(prompt, 0).clone()
+    assert torch.equal(l0, l1), "reset + prefill must reproduce the logits"
+    got, _ = dec.generate(first, 300, 10)
+    assert got == want
+    # up to the last cache position (four active attention splits), and not beyond it
+    long_prompt = torch.from_numpy(toks(500, cfg.vocab_size, 5)).cuda()
+    dec.reset()
+    f2 = int(dec.forward(long_prompt, 0).float().argmax().item())
+    got2, _ = dec.generate(f2, 500, 12)                       # positions 500..511
+    want2, tok, pos = [], f2, 500
+    dec.reset()
+    dec.forward(long_prompt, 0)
+    for _ in range(12):
+        tok = int(dec.forward(torch.tensor([tok], dtype=torch.int32, device="cuda"), pos).float().argmax().item())
+        want2.append(tok)
+        pos += 1
+    assert got2 == want2
+    with pytest.raises(tl.TllmError):
+        dec.generate(f2, 500, 13)
+    # the FP16 single-token path stays close to the INT8 one on the same model
+    dec.reset()
+    dec.forward(prompt, 0)
+    a = dec.forward(torch.tensor([first], dtype=torch.int32, device="cuda"), 300).clone()
+    dec16 = tl.Decoder(model, int8_decode=False)
+    dec16.forward(prompt, 0)
+    c = dec16.forward(torch.tensor([first], dtype=torch.int32, device="cuda"), 300).float()
+    assert (c - a.float()).abs().max().item() <= 0.15 * max(1.0, a.float().abs().max().item())
+    tl.check_device_errors()
+    dec.close()
+    dec16.close()
+
+
 def test_create_rejects_bad_models():
     cfg = cfg_small()
     model = tf.random_model(cfg, seed=1)
