@@ -751,13 +751,17 @@ def run_case(args):
         arch = dict(DECODE_ARCH_1B)
         if dims == "1b-4l":
             arch.update(n_layers=4, vocab_size=32000)
+        elif dims == "8b":      # LLaMA-3-8B architecture (the benchmark's GEMV shapes), weights drawn on the device
+            arch.update(hidden_dim=4096, intermediate_dim=14336, n_layers=32, n_heads=32, n_kv_heads=8, head_dim=128)
         elif dims != "1b":
             raise SystemExit(f"unknown decode architecture {dims}")
         n_prompt = int(rest[0]) if len(rest) > 0 else 512
         n_steps = int(rest[1]) if len(rest) > 1 else 128
         eager = len(rest) > 2 and rest[2] == "eager"
         cfg = tf.TllmConfig(**arch)
-        dec = tl.Decoder(tf.random_model(cfg, seed=2026), int8_decode=True)
+        model = synth.random_device_model(cfg, 2026, dev) if dims == "8b" else tf.random_model(cfg, seed=2026)
+        dec = tl.Decoder(model, int8_decode=True)
+        del model
         prompt = torch.from_numpy(np.random.default_rng(0).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)).to(dev)
         logits = dec.forward(prompt, 0)
         first = int(logits.float().argmax().item())
@@ -801,7 +805,7 @@ def main():
                     help="N>1 only: all-reduce fused into the row-parallel GEMV (default) or GEMV + NCCL")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--case", default="", help="run one small kernel case instead of the benchmark (for ncu): "
-                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemv_group:N1+N2xK[:copies] | gemm:MxNxK | decode:1b|1b-4l[:prompt[:steps[:eager]]] | decode_batch:1b|1b-4l:B[:prompt[:steps]]")
+                    "gemv:NxK[:copies] | gemv_int8:NxK[:copies] | gemv_group:N1+N2xK[:copies] | gemm:MxNxK | decode:1b|1b-4l|8b[:prompt[:steps[:eager]]] | decode_batch:1b|1b-4l:B[:prompt[:steps]]")
     args = ap.parse_args()
     if args.case:
         return run_case(args)

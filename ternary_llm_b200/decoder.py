@@ -35,10 +35,13 @@ class Decoder:
         staging = []             # ternary source arrays, needed only until create() has repacked them
 
         def up(a, keep=True):
-            a = np.array(a)      # copy: file views are read-only maps
-            if a.dtype == np.uint32:
-                a = a.view(np.int32)
-            t = torch.from_numpy(a).to(self.device)
+            if isinstance(a, torch.Tensor):          # already on the device (synth.random_device_model)
+                t = a.to(self.device).contiguous()
+            else:
+                a = np.array(a)  # copy: file views are read-only maps
+                if a.dtype == np.uint32:
+                    a = a.view(np.int32)
+                t = torch.from_numpy(a).to(self.device)
             (self._keep if keep else staging).append(t)
             return t.data_ptr()
 

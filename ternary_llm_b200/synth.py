@@ -44,3 +44,34 @@ def random_ternary_weight(rows: int, cols: int, seed: int, device, std: float = 
         w = torch.randn(r1 - r0, cols, generator=gen, device=device, dtype=torch.float32) * std
         nz[r0:r1], sg[r0:r1], sc[r0:r1] = ternarize_pack(w)
     return nz, sg, sc
+
+
+def random_device_model(cfg, seed: int, device, std: float = 0.02):
+    """tllm_format.random_model drawn on the device: the same structure (a TllmFile whose
+    arrays are CUDA tensors), for models too large to ternarise on the host in reasonable time.
+    Not bit-identical to random_model (different generator)."""
+    from .tllm_format import TernaryTensor, TllmFile, pad32
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def dense(rows, cols):
+        out = torch.empty(rows, cols, dtype=torch.float16, device=device)
+        for r0 in range(0, rows, 8192):
+            r1 = min(rows, r0 + 8192)
+            out[r0:r1] = (torch.randn(r1 - r0, cols, generator=gen, device=device) * std).to(torch.float16)
+        return out
+
+    m = TllmFile(cfg, dense(cfg.vocab_size, cfg.hidden_dim))
+    for li in range(cfg.n_layers):
+        layer = {}
+        for pi, (name, o, i) in enumerate(cfg.proj_shapes()):
+            layer[name] = TernaryTensor(*random_ternary_weight(o, i, seed=seed * 100003 + li * 16 + pi, device=device, std=std))
+        layer["attn_norm"] = torch.ones(cfg.hidden_dim, dtype=torch.float16, device=device)
+        layer["ffn_norm"] = torch.ones(cfg.hidden_dim, dtype=torch.float16, device=device)
+        m.layers.append(layer)
+    m.final_norm = torch.ones(cfg.hidden_dim, dtype=torch.float16, device=device)
+    if cfg.lm_head_ternary:
+        m.lm_head = TernaryTensor(*random_ternary_weight(cfg.vocab_size, pad32(cfg.hidden_dim), seed=seed * 100003 + 99991,
+                                                         device=device, std=std))
+    else:
+        m.lm_head = dense(cfg.vocab_size, cfg.hidden_dim)
+    return m
