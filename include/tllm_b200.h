@@ -166,7 +166,13 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
  * after the FFN norm (the reference issues them as separate calls on the same input,
  * src/transformer.cpp:206-222,271-283).  One launch streams all of them, so small
  * matrices (k, v) no longer pay a launch each; results equal those of `count` calls
- * of tllm_b200_gemv_packed up to the order of the FP32 additions over K.  packed, y, rows are HOST arrays of length count.
+ * of tllm_b200_gemv_packed up to the order of the FP32 additions over K.  packed, y, rows
+ * are HOST arrays of length count.
+ * Fastest when the matrices were packed back to back -- packed[i+1] == packed[i] +
+ * tllm_b200_packed_bytes(rows[i], cols) with every rows[i] but the last a multiple of 16
+ * (prepare them into consecutive pieces of one buffer): they are then streamed as ONE
+ * matrix.  Otherwise the launch walks the concatenated row blocks, or, for matrices that
+ * each fill the GPU on their own, falls back to one launch per matrix.
  */
 int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows,
                                 int cols, const void* x, void* stream);
