@@ -435,13 +435,25 @@ def run_ours(args):
     x_dev = x_host.to(dev)
     y_dev = torch.zeros(yo, dtype=torch.float16, device=dev)
 
-    def xs(i, k):
-        return x_dev[x_off[i]:x_off[i] + k]
+    # a second set of device buffers: the end-to-end loop overlaps the copies of one step with
+    # the kernels of the next (ping-pong), as a serving loop would
+    x_dev2 = torch.empty_like(x_dev)
+    y_dev2 = torch.zeros_like(y_dev)
+    y_host2 = torch.empty(yo, dtype=torch.float16).pin_memory()
 
-    def ys(i, n):
-        return y_dev[y_off[i]:y_off[i] + n]
+    def launch_step(xbuf=None, ybuf=None):
+        xbuf = x_dev if xbuf is None else xbuf
+        ybuf = y_dev if ybuf is None else ybuf
 
-    def launch_step():
+        def xs(i, k):
+            return xbuf[x_off[i]:x_off[i] + k]
+
+        def ys(i, n):
+            return ybuf[y_off[i]:y_off[i] + n]
+
+        return _launch_step(xs, ys)
+
+    def _launch_step(xs, ys):
         """One decode-style pass.  q/k/v read the same vector (as do gate/up), so they go
         through the fused entry point; o and down through the reference-signature call,
         which finds the prepared copy by the registered weight pointer."""
@@ -464,6 +476,9 @@ def run_ours(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             launch_step()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2, stream=stream):
+            launch_step(x_dev2, y_dev2)
 
         # roofline kernel: the dominant launch of the step, [gate|up] (28672 x 4096 as one matrix),
         # alone over the 32 distinct gate|up groups
@@ -507,18 +522,43 @@ def run_ours(args):
         barrier()
         ms = e0.elapsed_time(e1)
 
-        # ---- end to end: pinned host -> device, run, device -> pinned host ----------
-        for _ in range(max(1, args.warmup // 2)):
-            x_dev.copy_(x_host, non_blocking=True)
-            graph.replay()
-            y_host.copy_(y_dev, non_blocking=True)
+        # ---- end to end: pinned host -> device, run, device -> pinned host, every step ------------
+        # Three streams and two buffer sets: while step i computes, the inputs of step i+1 are
+        # copied in and the outputs of step i-1 are copied out.
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        bufs = [(x_dev, y_dev, y_host, graph), (x_dev2, y_dev2, y_host2, graph2)]
+        plain = lambda: torch.cuda.Event()
+
+        def e2e_loop(n):
+            done_c = [None, None]      # kernels of the last step that used buffer set b
+            done_o = [None, None]      # its outputs copied out
+            for i in range(n):
+                b = i & 1
+                xb, yb, yh, g = bufs[b]
+                if done_c[b] is not None:
+                    s_in.wait_event(done_c[b])          # the step that read xb has finished
+                with torch.cuda.stream(s_in):
+                    xb.copy_(x_host, non_blocking=True)
+                    ev_in = plain()
+                    ev_in.record(s_in)
+                stream.wait_event(ev_in)
+                if done_o[b] is not None:
+                    stream.wait_event(done_o[b])        # yb has been copied out
+                g.replay()
+                done_c[b] = plain()
+                done_c[b].record(stream)
+                s_out.wait_event(done_c[b])
+                with torch.cuda.stream(s_out):
+                    yh.copy_(yb, non_blocking=True)
+                    done_o[b] = plain()
+                    done_o[b].record(s_out)
+
+        e2e_loop(max(2, args.warmup // 2))
         barrier()
         f0, f1 = ev(), ev()
-        f0.record(stream)
-        for _ in range(args.steps):
-            x_dev.copy_(x_host, non_blocking=True)
-            graph.replay()
-            y_host.copy_(y_dev, non_blocking=True)
+        f0.record(s_in)
+        e2e_loop(args.steps)
+        stream.wait_stream(s_out)
         f1.record(stream)
         barrier()
         ms_e2e = f0.elapsed_time(f1)
@@ -601,7 +641,8 @@ def run_ours(args):
                          "warm_l2_us_per_launch": ms_warm * 1e3, "warm_l2_gbs": rb / (ms_warm * 1e-3) / 1e9,
                          "frac_of_nominal_8000": achieved / 8000.0},
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
-                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": ms_e2e / args.steps},
+                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": ms_e2e / args.steps,
+                    "overlap": "copies of neighbouring steps overlap the kernels (two buffer sets, three streams)"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "prefill_gemm": {"kernel": "tcgen05 kind::f16, weights expanded to exact FP16 in tensor memory",
