@@ -215,25 +215,116 @@ def random_model(cfg: TllmConfig, seed: int, std: float = 0.02) -> TllmFile:
     return m
 
 
-def load_projections(path: str, device, register: bool = False):
+TP_COLUMN = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")   # output rows are split
+TP_ROW = ("o_proj", "down_proj")                                      # input columns are split
+TP_GROUPS = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))  # share their input vector
+
+
+def shard_ternary(t: TernaryTensor, name: str, rank: int, world: int, group_size: int = 128) -> TernaryTensor:
+    """The part of projection `name` that rank `rank` of `world` tensor-parallel ranks holds.
+
+    q, k, v, gate and up are column-parallel: a contiguous range of output rows of all three
+    arrays (a pointer offset in the file's layout).  o and down are row-parallel: a range of
+    input columns on group boundaries, i.e. strided slices of all three arrays; their partial
+    results are summed across ranks.  The shards are views of `t`."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    rows, cols = t.shape
+    if world == 1:
+        return t
+    if name in TP_COLUMN:
+        if rows % world:
+            raise ValueError(f"{name}: {rows} rows do not split over {world} ranks")
+        r0, r1 = rank * (rows // world), (rank + 1) * (rows // world)
+        return TernaryTensor(t.nonzero_masks[r0:r1], t.sign_masks[r0:r1], t.scales[r0:r1])
+    if name in TP_ROW:
+        if cols % (world * group_size):
+            raise ValueError(f"{name}: {cols} columns do not split over {world} ranks on {group_size}-column groups")
+        k0, k1 = rank * (cols // world), (rank + 1) * (cols // world)
+        return TernaryTensor(t.nonzero_masks[:, k0 // 32:k1 // 32], t.sign_masks[:, k0 // 32:k1 // 32],
+                             t.scales[:, k0 // group_size:k1 // group_size])
+    raise ValueError(f"unknown projection {name}")
+
+
+class _PinnedStager:
+    """Host-to-device copies through two page-locked buffers used in turn: the copy of one
+    array runs while the host gathers the next one (a row-parallel shard is a strided slice
+    of the memory-mapped file) into the other buffer."""
+
+    def __init__(self, torch, device, nbytes: int):
+        self.torch, self.device = torch, device
+        self.bufs = [torch.empty(max(nbytes, 16), dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.events = [None, None]
+        self.turn = 0
+
+    def to_device(self, a: np.ndarray):
+        torch = self.torch
+        i, self.turn = self.turn, self.turn ^ 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()          # the buffer's previous copy has left it
+        n = a.nbytes
+        host = self.bufs[i][:n]
+        np.copyto(host.numpy().view(a.dtype).reshape(a.shape), a)
+        dt = {"uint32": torch.int32, "float16": torch.float16}[a.dtype.name]
+        out = torch.empty(a.shape, dtype=dt, device=self.device)
+        out.view(torch.uint8).reshape(-1).copy_(host, non_blocking=True)
+        self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+        return out
+
+
+def load_projections(path: str, device, register: bool = False, rank: int = 0, world: int = 1,
+                     verify: bool = False, grouped: bool = False):
     """Reads a .tllm file and prepares every ternary projection on `device` for the
     streaming kernels (the load-time repack).  Returns (config, layers) where layers[i]
     maps a projection name to an ops.PreparedWeight.  Projections whose input width is
-    not a multiple of 128 are rejected by the library (TllmError)."""
+    not a multiple of 128 are rejected by the library (TllmError).
+
+    rank, world: load only this tensor-parallel rank's shard of every projection
+        (shard_ternary); nothing of the other ranks' parts is copied to the device.
+    verify: unpack every prepared matrix again and compare it bit for bit with what was read.
+    grouped: pack q|k|v and gate|up back to back, so that ternary_gemv_packed_multi runs
+        each group as one launch (ops.prepare_group).
+    The arrays go to the device through page-locked staging buffers."""
     import torch
 
     from . import ops
+    if register and grouped:
+        raise ValueError("grouped weights are not registered under their source arrays")
     m = read_tllm(path)
+    gs = m.config.group_size
+    shards = [{name: shard_ternary(layer[name], name, rank, world, gs) for name in PROJ_NAMES} for layer in m.layers]
+    biggest = max(t.nonzero_masks.size * 4 for d in shards for t in d.values()) if shards else 0
+    stager = _PinnedStager(torch, torch.device(device), biggest)
+
+    def device_arrays(t):
+        rows, cols = t.shape
+        return (stager.to_device(t.nonzero_masks), stager.to_device(t.sign_masks), stager.to_device(t.scales),
+                rows, cols)
+
+    def check(w, src, what):
+        nz, sg, sc = w.unpack()
+        if not (torch.equal(nz, src[0]) and torch.equal(sg, src[1])
+                and torch.equal(sc.view(torch.int16), src[2].view(torch.int16))):
+            raise ValueError(f"{what}: the prepared matrix does not unpack to the arrays of the file")
+
     out = []
-    for layer in m.layers:
+    for li, layer in enumerate(shards):
         d = {}
-        for name in PROJ_NAMES:
-            t = layer[name]
-            rows, cols = t.shape
-            # copies: the file views are read-only memory maps
-            nz = torch.from_numpy(np.array(t.nonzero_masks).view(np.int32)).to(device)
-            sg = torch.from_numpy(np.array(t.sign_masks).view(np.int32)).to(device)
-            sc = torch.from_numpy(np.array(t.scales)).to(device)
-            d[name] = ops.PreparedWeight(nz, sg, sc, rows, cols, register=register, keep_source=register)
+        todo = list(PROJ_NAMES)
+        if grouped:
+            for names in TP_GROUPS:
+                srcs = [device_arrays(layer[n]) for n in names]
+                for n, w, src in zip(names, ops.prepare_group(srcs), srcs):
+                    d[n] = w
+                    if verify:
+                        check(w, src, f"layer {li} {n}")
+                    todo.remove(n)
+        for name in todo:
+            src = device_arrays(layer[name])
+            d[name] = ops.PreparedWeight(*src, register=register, keep_source=register)
+            if verify:
+                check(d[name], src, f"layer {li} {name}")
         out.append(d)
+    torch.cuda.synchronize(torch.device(device))
     return m.config, out

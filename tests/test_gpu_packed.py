@@ -236,6 +236,51 @@ def test_tllm_file_to_prepared_weights(tmp_path):
             assert_within(y, y64, bound, f"L{li}.{name}", slack=_half_ulp(y64))
 
 
+def test_tllm_file_sharded_load(tmp_path):
+    """Shard-at-load: two tensor-parallel ranks' loads of one file (verified repack, q|k|v and
+    gate|up grouped) reassemble every projection -- column shards stacked, row shards summed."""
+    from ternary_llm_b200 import tllm_format as tf
+    cfg = tf.TllmConfig(vocab_size=64, hidden_dim=512, intermediate_dim=1024, n_layers=1, n_heads=8,
+                        n_kv_heads=2, head_dim=64, max_seq_len=64)
+    m = tf.random_model(cfg, seed=12)
+    path = str(tmp_path / "tp.tllm")
+    tf.write_tllm(path, m)
+    world = 2
+    ranks = [tf.load_projections(path, DEV, rank=r, world=world, verify=True, grouped=True)[1][0] for r in range(world)]
+    for r in range(world):      # grouped: the packed matrices of a group lie back to back
+        q, k, v = (ranks[r][n] for n in ("q_proj", "k_proj", "v_proj"))
+        assert k.packed.data_ptr() == q.packed.data_ptr() + q.packed.numel()
+        assert v.packed.data_ptr() == k.packed.data_ptr() + k.packed.numel()
+    rng = np.random.default_rng(6)
+    for name, rows, cols in cfg.proj_shapes():
+        t = m.layers[0][name]
+        x = rng.standard_normal((1, cols)).astype(np.float16)
+        y64, bound = exact_and_bound(t.nonzero_masks, t.sign_masks, t.scales, x)
+        if name in tf.TP_COLUMN:
+            assert all(ranks[r][name].rows == rows // world and ranks[r][name].cols == cols for r in range(world))
+            y = np.concatenate([_run_packed(ranks[r][name], x) for r in range(world)], axis=-1)
+            assert_within(y, y64, bound, name, slack=_half_ulp(y64))
+        else:
+            kw = cols // world
+            assert all(ranks[r][name].rows == rows and ranks[r][name].cols == kw for r in range(world))
+            parts = [_run_packed(ranks[r][name], np.ascontiguousarray(x[:, r * kw:(r + 1) * kw])).astype(np.float64)
+                     for r in range(world)]
+            # each partial result is rounded to FP16 once before the sum
+            assert_within(sum(parts), y64, bound, name, slack=sum(_half_ulp(p) for p in parts))
+    # the fused launch over a group read through the loader's layout
+    x = torch.randn(cfg.hidden_dim, device=DEV).half()
+    g = [ranks[1][n] for n in ("gate_proj", "up_proj")]
+    ys = [torch.zeros(w.rows, dtype=torch.float16, device=DEV) for w in g]
+    tl.ternary_gemv_packed_multi(g, x, ys)
+    for w, y in zip(g, ys):
+        y1 = torch.zeros_like(y)
+        tl.ternary_gemv_packed(w, x, y1, 1)
+        torch.cuda.synchronize()
+        assert (y.float() - y1.float()).abs().max().item() <= 2.0 ** -10 * max(1.0, y1.float().abs().max().item())
+    with pytest.raises(ValueError):
+        tf.load_projections(path, DEV, rank=0, world=16)       # 512 columns / 16 ranks is no whole group
+
+
 def test_group_packed_back_to_back_runs_as_one_matrix():
     """prepare_group + the fused entry points: same results as one call per matrix, FP16 and INT8."""
     from ternary_llm_b200 import layer_ops, synth

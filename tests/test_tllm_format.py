@@ -78,3 +78,50 @@ def test_reference_offset_checker_accepts_the_file(tmp_path):
                          capture_output=True, text=True, check=True).stdout
     assert "MISMATCH" not in out and "Looks valid" in out
     assert "Tokenizer size at expected position: 100 bytes" in out
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_tensor_parallel_shards_reassemble_the_projection(world):
+    """Column shards stacked and row shards summed give the unsharded oracle result; the
+    shards' unpacked ternary values are the corresponding slices bit for bit."""
+    from oracle import oracle
+    cfg = tf.TllmConfig(**{**CFG.__dict__, "hidden_dim": 512, "intermediate_dim": 1024, "n_heads": 8, "n_layers": 1,
+                           "vocab_size": 32})
+    m = tf.random_model(cfg, seed=9)
+    rng = np.random.default_rng(21)
+    for name, rows, cols in cfg.proj_shapes():
+        t = m.layers[0][name]
+        x = rng.standard_normal(cols).astype(np.float16)
+        full = oracle.ternary_matvec(t.nonzero_masks, t.sign_masks, t.scales, x, 128, np.float64)
+        tern = oracle.unpack_bitmasks(t.nonzero_masks, t.sign_masks)
+        parts = [tf.shard_ternary(t, name, r, world) for r in range(world)]
+        c = np.ascontiguousarray
+        if name in tf.TP_COLUMN:
+            assert all(p.shape == (rows // world, cols) for p in parts)
+            y = np.concatenate([oracle.ternary_matvec(c(p.nonzero_masks), c(p.sign_masks), c(p.scales), x, 128,
+                                                      np.float64) for p in parts])
+            assert np.array_equal(y, full)
+            got = np.concatenate([oracle.unpack_bitmasks(c(p.nonzero_masks), c(p.sign_masks)) for p in parts], 0)
+        else:
+            assert name in tf.TP_ROW and all(p.shape == (rows, cols // world) for p in parts)
+            kw = cols // world
+            y = sum(oracle.ternary_matvec(c(p.nonzero_masks), c(p.sign_masks), c(p.scales), x[r * kw:(r + 1) * kw],
+                                          128, np.float64) for r, p in enumerate(parts))
+            bound = oracle.tolerance_bound(t.nonzero_masks, t.sign_masks, t.scales, x)
+            assert (np.abs(y - full) <= 1e-9 * bound + 1e-12).all()
+            got = np.concatenate([oracle.unpack_bitmasks(c(p.nonzero_masks), c(p.sign_masks)) for p in parts], 1)
+        assert np.array_equal(got, tern)
+
+
+def test_shards_that_do_not_divide_are_rejected():
+    m = tf.random_model(CFG, seed=9)
+    layer = m.layers[0]
+    with pytest.raises(ValueError):
+        tf.shard_ternary(layer["o_proj"], "o_proj", 0, 4)        # 256 columns: 64 per rank is no whole group
+    with pytest.raises(ValueError):
+        tf.shard_ternary(layer["k_proj"], "k_proj", 0, 3)
+    with pytest.raises(ValueError):
+        tf.shard_ternary(layer["q_proj"], "q_proj", 2, 2)
+    with pytest.raises(ValueError):
+        tf.shard_ternary(layer["q_proj"], "lm_head", 0, 2)
+    assert tf.shard_ternary(layer["q_proj"], "q_proj", 0, 1) is layer["q_proj"]
