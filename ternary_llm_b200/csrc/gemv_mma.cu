@@ -86,6 +86,8 @@ struct GemvArgs {
     int batch;              // 1 or 2 vectors handled by this launch
     int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
     int aligned;            // 1: items are whole row blocks (no block spans two CTAs); 0: items are tiles
+    int late_release;       // 1: the next kernel in the stream is released after this kernel's own dependency
+                            //    wait instead of at its start (see release_rule)
     float* ws;              // [gridDim.x][2][16][2] partial records of this ticket
     int* counters;          // [row blocks] arrival counters of this ticket (zero between launches)
     int* err;               // device error flag (0 = none)
@@ -97,6 +99,23 @@ struct GemvArgs {
     uint2* ar_recv[kMaxPeers];        // rank d's receive buffer  {value, launch number} [2][world][ar_rows_max]
     unsigned* ar_epoch;               // this rank's launch counters, uint [kMaxCtas]
 };
+
+// When a launch releases the next kernel of the stream.  Released at its start, the next
+// kernel (and, through it, the one after) becomes resident while this one still runs and
+// prefetches its own weights: a long stream of large matrices gains from that depth.  A small
+// matrix lives on latencies, and the prefetch traffic of kernels two launches ahead queues in
+// front of its activation loads and its final stores; such a launch releases its successor only
+// after its own dependency wait, which bounds the look-ahead to one kernel.  Measured on a
+// decode step of 2048-wide layers: 2.3 % faster per token with the late release, while the
+// 4096-wide benchmark sweep is 4 % slower if its matrices of 16 MB and more are released late.
+#ifndef TLLM_LATE_RELEASE_BYTES
+#define TLLM_LATE_RELEASE_BYTES (10u << 20)
+#endif
+static inline int release_rule(int rows, int cols)
+{
+    const size_t bytes = (size_t)((rows + 15) / 16) * (size_t)(cols / kGroup) * (size_t)kTileBytes;
+    return bytes <= (size_t)TLLM_LATE_RELEASE_BYTES ? 1 : 0;
+}
 
 #ifdef TLLM_PROFILE_PHASES
 __device__ unsigned long long g_phase_ns[kMaxCtas * 16];
@@ -452,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     constexpr bool I8 = (MODE == kI8 || FUSEDX);
     constexpr int LANES = (MODE == kF16B2) ? 32 : 16;
 
-    asm volatile("griddepcontrol.launch_dependents;");
+    if (!a.late_release) asm volatile("griddepcontrol.launch_dependents;");
     PHASE(0);
     TL_MARK(MODE, 0);
 
@@ -500,6 +519,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_packed_kernel(const
     // ---- everything below may depend on the previous kernel in the stream -------
     PHASE(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (a.late_release) asm volatile("griddepcontrol.launch_dependents;");
     PHASE(2);
     TL_MARK(MODE, 1);
 
@@ -1208,6 +1228,7 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     if (items < grid) grid = items;
     a.part_q = items / grid;
     a.part_r = items % grid;
+    a.late_release = release_rule(rows, cols);
     unsigned ticket;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -1514,6 +1535,7 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     if (items < grid) grid = items;
     a.part_q = items / grid;
     a.part_r = items % grid;
+    a.late_release = release_rule(rows, cols);
     a.ws = reinterpret_cast<float*>(nd.base);
     a.counters = reinterpret_cast<int*>(nd.base + kNoAllocWsBytes);
     a.err = reinterpret_cast<int*>(nd.base + kNoAllocWsBytes + kNoAllocCounterBytes);
