@@ -291,7 +291,7 @@ attention_kernel(const AttnArgs a)
 // ---------------------------------------------------------------------------
 // What the reference does with rope_forward, copy_to_kv_cache and attention_forward
 // (src/transformer.cpp:225-245) for one new token.  Grid (splits, KV heads); a CTA owns
-// 128 cache positions of one KV head and the query heads that share it.  After the
+// 64 cache positions of one KV head and the query heads that share it.  After the
 // dependency wait the CTA immediately requests its slice of K and V (bulk copies of the
 // positions written by earlier steps), and while they fly it rotates the group's queries
 // into shared memory; the CTA whose slice holds the new position also rotates the new key,
@@ -299,7 +299,7 @@ attention_kernel(const AttnArgs a)
 // softmax as in attention_kernel; P.V runs with one thread per (head, channel pair) and
 // several position groups in parallel, reduced through shared memory.  Splits merge through
 // the last-arriver scheme of attention_kernel.
-constexpr int kDecChunk = 128;
+constexpr int kDecChunk = 64;
 constexpr int kDecMaxItems = 8;       // (head, channel pair) items per thread
 
 struct DecodeArgs {
