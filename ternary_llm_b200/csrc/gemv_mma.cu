@@ -353,8 +353,11 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, int8_t* xq, ha
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             if (MODE == kI8Silu) {
+                // The reference's release build compiles its SiLU with --use_fast_math
+                // (CMakeLists.txt:21; kernels/activations.cu:44), i.e. with these intrinsics.  The
+                // exact forms cost every CTA about a microsecond per 8192 elements here.
                 const float g = __half2float(ah[j]);
-                sth[j] = __float2half_rn(g / (1.0f + expf(-g)) * __half2float(bh[j]));
+                sth[j] = __float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * __half2float(bh[j]));
                 mx = fmaxf(mx, fabsf(__half2float(sth[j])));
             } else if (MODE == kI8Quant) {
                 sth[j] = ah[j];
