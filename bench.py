@@ -690,7 +690,7 @@ def decode_sample(torch, tl, dev, n_prompt=512, n_steps=128):
     return {"workload": "LLaMA-3.2-1B architecture, seeded random weights, 512-token prefill then 128 greedy steps, batch 1",
             "prefill_ms": e0.elapsed_time(e1), "decode_ms_per_token": ms, "tok_per_s": 1e3 / ms,
             "weight_bytes_per_token": step_bytes, "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9,
-            "launches_per_token": cfg.n_layers * 5 + 5,
+            "launches_per_token": cfg.n_layers * 5 + 4,   # + embedding, final norm, lm_head, argmax (advances the position)
             "arithmetic": "INT8 activations for single-token steps (the reference engine's choice), FP16 + tcgen05 GEMM for the prefill"}
 
 

@@ -473,10 +473,8 @@ int tllm_b200_decoder_generate(void* decoder, int first_token, int start_pos, in
     auto step = [&]() -> int {
         int e = forward(D, D->state, 1, 0, D->state + 1, 0, 0, s);
         if (e) return e;
-        if ((e = launch_argmax(D->logits, D->d.vocab_size, D->state, D->history, D->state + 2, D->am_val, D->am_idx,
-                               D->am_counter, s)))
-            return e;
-        return launch_advance(D->state + 1, 1, s);
+        return launch_argmax(D->logits, D->d.vocab_size, D->state, D->history, D->state + 2, D->am_val, D->am_idx,
+                             D->am_counter, D->state + 1, s);
     };
     if (!D->step_graph) {
         // One eager step first: it performs every lazy set-up (scratch allocation, kernel

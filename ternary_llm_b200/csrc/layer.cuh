@@ -24,10 +24,10 @@ int launch_fp16_gemv(const half* w, const half* x, half* y, int rows, int cols, 
 // y[b, r] = W[r, :] . x[b, :] for `batch` vectors (x [batch, cols], y [batch, rows]).
 int launch_fp16_gemv_batched(const half* w, const half* x, half* y, int batch, int rows, int cols, cudaStream_t stream);
 int launch_fp16_gemm(const half* A, const half* B, half* C, int M, int N, int K, cudaStream_t stream);
-// part_val / part_idx: 64 entries each; counter: one zero-initialised unsigned.
+// part_val / part_idx: 64 entries each; counter: one zero-initialised unsigned; pos: when not
+// null, *pos is advanced by one together with the token (the decode loop's cache position).
 int launch_argmax(const half* logits, int n, int* out, int* history, int* step, float* part_val, int* part_idx,
-                  unsigned* counter, cudaStream_t stream);
-int launch_advance(int* pos, int by, cudaStream_t stream);
+                  unsigned* counter, int* pos, cudaStream_t stream);
 
 size_t attention_workspace_bytes(int batch, int n_heads, int n_kv_heads, int head_dim, int kv_len_max);
 // kv_len_dev: decode only, kv_len = kv_len + *kv_len_dev.  ws / counters: decode split scratch or null.

@@ -616,7 +616,7 @@ constexpr int kArgmaxThreads = 256;
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const half* __restrict__ logits, int n, int* __restrict__ out, int* __restrict__ history,
               int* __restrict__ step, float* __restrict__ part_val, int* __restrict__ part_idx,
-              unsigned* __restrict__ counter)
+              unsigned* __restrict__ counter, int* __restrict__ pos)
 {
     __shared__ float sv[kArgmaxThreads / 32];
     __shared__ int si[kArgmaxThreads / 32];
@@ -683,30 +683,16 @@ argmax_kernel(const half* __restrict__ logits, int n, int* __restrict__ out, int
             history[*step] = idx;
             *step = *step + 1;
         }
+        if (pos) *pos = *pos + 1;      // the decode loop's cache position moves on with the token
         *counter = 0;
     }
 }
 
 int launch_argmax(const half* logits, int n, int* out, int* history, int* step, float* part_val, int* part_idx,
-                  unsigned* counter, cudaStream_t stream)
+                  unsigned* counter, int* pos, cudaStream_t stream)
 {
     return launch_pdl("argmax", argmax_kernel, dim3(kArgmaxCtas), dim3(kArgmaxThreads), 0, stream, logits, n, out,
-                      history, step, part_val, part_idx, counter);
-}
-
-// Advances the device-side position of a graph-replayed decode step.
-__global__ void advance_kernel(int* pos, int by)
-{
-    pdl_launch_dependents();
-    TL_MARK(34, 0);
-    pdl_wait();
-    TL_MARK(34, 1);
-    if (threadIdx.x == 0) *pos += by;
-}
-
-int launch_advance(int* pos, int by, cudaStream_t stream)
-{
-    return launch_pdl("advance", advance_kernel, dim3(1), dim3(32), 0, stream, pos, by);
+                      history, step, part_val, part_idx, counter, pos);
 }
 
 }  // namespace tllm
