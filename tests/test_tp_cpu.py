@@ -11,6 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import oracle
+from ternary_llm_b200 import tllm_format as tf
 
 
 def _free_port():
@@ -26,9 +27,11 @@ def _worker(rank, world, port, n, k, out):
     full = oracle.ternary_matvec(nz, sg, sc, x[0], 128, np.float64)
     t_full = oracle.unpack_bitmasks(nz, sg)
 
-    # column-parallel: contiguous row ranges of all three arrays
+    # column-parallel: contiguous row ranges of all three arrays (the loader's shard_ternary)
     r0, r1 = rank * n // world, (rank + 1) * n // world
-    y_col = oracle.ternary_matvec(nz[r0:r1], sg[r0:r1], sc[r0:r1], x[0], 128, np.float64)
+    col = tf.shard_ternary(tf.TernaryTensor(nz, sg, sc), "q_proj", rank, world)
+    assert np.array_equal(col.nonzero_masks, nz[r0:r1]) and np.array_equal(col.scales, sc[r0:r1])
+    y_col = oracle.ternary_matvec(col.nonzero_masks, col.sign_masks, col.scales, x[0], 128, np.float64)
     gathered = [torch.zeros(r1 - r0, dtype=torch.float64) for _ in range(world)]
     dist.all_gather(gathered, torch.from_numpy(y_col))
     ok_col = np.array_equal(torch.cat(gathered).numpy(), full)
@@ -37,8 +40,9 @@ def _worker(rank, world, port, n, k, out):
     # row-parallel: K ranges on 128-aligned boundaries, partial sums all-reduced
     k0, k1 = rank * k // world, (rank + 1) * k // world
     assert k0 % 128 == 0 and k1 % 128 == 0
-    nzs, sgs = nz[:, k0 // 32:k1 // 32], sg[:, k0 // 32:k1 // 32]
-    scs = sc[:, k0 // 128:k1 // 128]
+    row = tf.shard_ternary(tf.TernaryTensor(nz, sg, sc), "o_proj", rank, world)
+    nzs, sgs, scs = row.nonzero_masks, row.sign_masks, row.scales
+    assert nzs.shape == (n, (k1 - k0) // 32) and np.array_equal(scs, sc[:, k0 // 128:k1 // 128])
     part = torch.from_numpy(oracle.ternary_matvec(np.ascontiguousarray(nzs), np.ascontiguousarray(sgs),
                                                   np.ascontiguousarray(scs), x[0, k0:k1], 128, np.float64))
     dist.all_reduce(part)
