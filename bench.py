@@ -204,7 +204,7 @@ METRIC_TP = "ternary_gemv_hbm_throughput_llama70b_shapes_tp_batch1"
 def tp_shapes(tp: int):
     """Per-rank (name, rows, cols) of one layer: q/k/v/gate/up are column-parallel
     (rows split), o/down are row-parallel (cols split on 128-aligned boundaries)."""
-    assert Q70 % (16 * tp) == 0 and KV70 % (16 * tp) == 0 and I70 % (128 * tp) == 0 and H70 % (128 * tp) == 0
+    assert Q70 % (64 * tp) == 0 and KV70 % (64 * tp) == 0 and I70 % (128 * tp) == 0 and H70 % (128 * tp) == 0
     return [("q", Q70 // tp, H70), ("k", KV70 // tp, H70), ("v", KV70 // tp, H70), ("o", H70, Q70 // tp),
             ("gate", I70 // tp, H70), ("up", I70 // tp, H70), ("down", H70, I70 // tp)]
 

@@ -110,9 +110,9 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B,
 /* ------------------------------------------------------------------------
  * Prepared weights (load-time repack).
  *
- * The streaming tensor-core GEMV reads a kernel-friendly layout: tiles of 16 rows
- * x 128 columns, 2 bits per weight arranged as operand selectors, FP16 scales
- * beside them (ternary_llm_b200/csrc/packed_layout.cuh).  It is derived once per
+ * The streaming tensor-core GEMV reads a kernel-friendly layout: super-tiles of 64 rows
+ * x 128 columns, 2 bits per weight (offset codes t + 1 arranged so that one AND makes an
+ * MMA operand register), FP16 scales beside them (ternary_llm_b200/csrc/packed_layout.cuh).  It is derived once per
  * matrix at load time from the three reference arrays -- the hook sits right
  * after the reference loader's read_ternary_weight (src/model.cpp:46-60) -- and is
  * lossless for canonical masks (no sign bit without its nonzero bit), which is
@@ -121,7 +121,8 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B,
  * stray sign bits is refused (TLLM_ERR_NONCANON) and stays on the general path.
  * ------------------------------------------------------------------------ */
 
-/* Size in bytes of the packed form of a [rows, cols] matrix (cols % 128 == 0). */
+/* Size in bytes of the packed form of a [rows, cols] matrix (cols % 128 == 0); rows are
+ * padded to a multiple of 64 in it. */
 size_t tllm_b200_packed_bytes(int rows, int cols);
 
 /*
@@ -169,10 +170,9 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
  * of tllm_b200_gemv_packed up to the order of the FP32 additions over K.  packed, y, rows
  * are HOST arrays of length count.
  * Fastest when the matrices were packed back to back -- packed[i+1] == packed[i] +
- * tllm_b200_packed_bytes(rows[i], cols) with every rows[i] but the last a multiple of 16
+ * tllm_b200_packed_bytes(rows[i], cols) with every rows[i] but the last a multiple of 64
  * (prepare them into consecutive pieces of one buffer): they are then streamed as ONE
- * matrix.  Otherwise the launch walks the concatenated row blocks, or, for matrices that
- * each fill the GPU on their own, falls back to one launch per matrix.
+ * matrix in one launch.  Otherwise one launch per matrix.
  */
 int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows,
                                 int cols, const void* x, void* stream);
@@ -190,9 +190,10 @@ int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* cons
  *   peer_recv[d] : rank d's receive buffer, 8-byte words [2][world][rows_max], as mapped in
  *                  THIS process (peer / symmetric memory), zeroed before first use
  *   epoch_local  : this rank's launch counters, uint32 [TLLM_AR_MAX_CTAS], zeroed
- * All ranks must issue the same sequence of these calls.  rows >= 16 x (number of SMs);
- * otherwise TLLM_ERR_SHAPE (use tllm_b200_gemv_packed + a library all-reduce).  A wait
- * that expires sets the device error flag (tllm_b200_check_device_errors).
+ * All ranks must issue the same sequence of these calls.  Each CTA owns whole 64-row
+ * blocks (one block per CTA while rows <= 64 x number of SMs).  A wait that expires sets
+ * the device error flag (tllm_b200_check_device_errors); after the first one that expires
+ * in a CTA, its remaining waits of that launch return at once.
  */
 int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, int rows, int cols,
                                     int rank, int world, void* const* peer_recv, void* epoch_local,
@@ -203,7 +204,7 @@ int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, 
  * allocate device memory (a server that owns all of HBM through its own arena, a
  * real-time loop, a host that audits allocations up front).  It has no counterpart
  * in the reference.  Nothing is allocated, by this call or any routine it uses: the
- * split-K scratch is a fixed 82 KB array inside the library image, present on every
+ * split-K scratch is a fixed 84 KB array inside the library image, present on every
  * GPU that loads the library until the process exits.
  * Limits: rows <= 65536 (TLLM_ERR_SIZE beyond), cols as for tllm_b200_gemv_packed.
  * The first call on a device resolves the array's device address and configures the
@@ -216,8 +217,17 @@ int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y,
                                   int rows, int cols, void* stream);
 
 /*
+ * Error report for tllm_b200_gemv_packed_noalloc, equally allocation-free (the regular
+ * tllm_b200_check_device_errors reads a flag in the library's allocated scratch and may
+ * set that scratch up).  SYNCHRONISES `stream`, returns TLLM_ERR_TIMEOUT if a bounded wait
+ * of a no-allocation launch expired since the last check (and clears the flag, which lives
+ * in the same fixed array), else TLLM_OK.  No counterpart in the reference.
+ */
+int tllm_b200_gemv_packed_noalloc_status(void* stream);
+
+/*
  * Prefill GEMM on prepared weights: C[M,N] = A[M,K] . W^T, same contract as
- * tllm_b200_gemm.  M > 6 runs the tcgen05 tensor-core kernel (weights expanded to
+ * tllm_b200_gemm.  M > 8 runs the tcgen05 tensor-core kernel (weights expanded to
  * exact FP16 {-s,0,+s} in tensor memory, FP32 accumulation in TMEM; token tile 32, 64,
  * 128 or 256 by M); smaller M runs passes of the streaming GEMV.  tllm_b200_gemm reaches the same kernels when
  * the weight pointer has been registered.

@@ -17,8 +17,10 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# Where a checkout of the reference project is looked for (optional; only build steps use it).
-REF_DIR = os.environ.get("TLLM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+# Where a checkout of the reference project is looked for (optional; only build steps use
+# it): the directory named by TLLM_REFERENCE_DIR, else a directory `reference` beside this
+# repository's own directory.
+REF_DIR = os.environ.get("TLLM_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 _PORT = os.path.join(_HERE, "liboracle_cpu.so")
 _REF = os.path.join(_HERE, "_ref", "libref.so")
 

@@ -34,6 +34,7 @@ SIGNATURES = {
     "tllm_b200_check_device_errors": (_int, [_vp]),
     "tllm_b200_gemm_packed": (_int, [_vp] * 3 + [_int] * 3 + [_vp]),
     "tllm_b200_gemv_packed_noalloc": (_int, [_vp] * 3 + [_int] * 2 + [_vp]),
+    "tllm_b200_gemv_packed_noalloc_status": (_int, [_vp]),
     "tllm_b200_gemv_packed_allreduce": (_int, [_vp] * 3 + [_int] * 4 + [_vp] * 2 + [_int, _vp]),
     "tllm_b200_gemv_packed_multi": (_int, [_int, _vp, _vp, _vp, _int, _vp, _vp]),
     # include/tllm_b200_layer.h

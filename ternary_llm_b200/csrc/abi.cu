@@ -45,8 +45,9 @@ int check_device()
     return TLLM_OK;
 }
 
-// Largest token count served by passes of the streaming GEMV; above it the tcgen05 kernel.
-constexpr int kGemvMaxBatch = 6;
+// Largest token count served by passes of the streaming GEMV (four vectors per pass over the
+// weights); above it the tcgen05 kernel, which reads the weights once for the whole batch.
+constexpr int kGemvMaxBatch = 8;
 
 static inline bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
@@ -101,9 +102,8 @@ int tllm_b200_gemv_batched(const uint32_t* nz, const uint32_t* sg, const void* s
     if (misaligned(y, 2)) return fail(TLLM_ERR_ALIGN, "output pointer must be 2-byte aligned");
     if ((st = check_device())) return st;
     if (const uint8_t* packed = lookup_packed(nz, rows, cols)) {
-        // up to six vectors: the streaming GEMV (two share one weight pass); more: the
+        // up to eight vectors: the streaming GEMV (four share one weight pass); more: the
         // tensor-core kernel with a 32-token tile reads the weights once for the whole batch
-        // (measured cross-over on the 8B shapes)
         if (batch > kGemvMaxBatch && gemm_tcgen05_supported(batch, rows, cols))
             return launch_gemm_tcgen05((const half*)x, packed, (half*)y, batch, rows, cols, (cudaStream_t)stream);
         return launch_gemv_packed(packed, (const half*)x, (half*)y, batch, rows, cols, (cudaStream_t)stream);
@@ -277,6 +277,13 @@ int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y, in
     if (st) return st;
     return launch_gemv_packed_noalloc((const uint8_t*)packed, (const half*)x, (half*)y, rows, cols,
                                       (cudaStream_t)stream);
+}
+
+int tllm_b200_gemv_packed_noalloc_status(void* stream)
+{
+    int st = check_device();
+    if (st) return st;
+    return noalloc_error_check((cudaStream_t)stream);
 }
 
 int tllm_b200_gemm_packed(const void* A, const void* packed, void* C, int M, int N, int K, void* stream)

@@ -324,7 +324,6 @@ attention_decode_kernel(const DecodeArgs a)
 {
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
-    TL_MARK(20, 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, hp = hd >> 1;
     const int G = a.n_heads / a.n_kv_heads;
@@ -358,7 +357,6 @@ attention_decode_kernel(const DecodeArgs a)
     __syncthreads();
 
     pdl_wait();
-    TL_MARK(20, 1);
     const int pos = a.pos_dev ? *a.pos_dev : a.pos;
     const int limit = pos + 1;
     int nactive = (limit + kDecChunk - 1) / kDecChunk;
@@ -561,7 +559,6 @@ attention_decode_kernel(const DecodeArgs a)
         __syncthreads();
     }
 
-    TL_MARK(20, 2);
     // ---- reduce the position groups, then write or publish ------------------------------
     if (pgroups > 1) {
         const int item = tid % items, pg = tid / items;
@@ -751,4 +748,3 @@ int launch_attention(const half* q, const half* k_cache, const half* v_cache, ha
 
 }  // namespace tllm
 
-TL_DUMP(tllm_b200_debug_timeline_attention)

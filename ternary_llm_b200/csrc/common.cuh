@@ -31,6 +31,9 @@ int launch_quantize_absmax_int8(const half* x, int8_t* q, float* scale, int n,
 
 // Tensor-core streaming kernels on the packed layout (gemv_mma.cu).
 size_t packed_bytes(int rows, int cols);
+// Row counts that are a multiple of this pack without padding (matrices packed back to back
+// can then be streamed as one).
+int packed_row_align();
 const uint8_t* lookup_packed(const void* nz, int rows, int cols);
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
                        cudaStream_t stream);
@@ -63,6 +66,7 @@ int launch_gemv_int8_packed_silu(const uint8_t* packed, const half* gate, const 
 int launch_gemv_int8_packed_quant(const uint8_t* packed, const half* x, half* y, int rows, int cols, cudaStream_t stream);
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream);
+int noalloc_error_check(cudaStream_t stream);
 
 // tcgen05 prefill GEMM on prepared weights (gemm_tcgen05.cu).
 bool gemm_tcgen05_supported(int M, int N, int K);

@@ -114,7 +114,7 @@ int pack_group(Decoder* D, int count, const tllm_b200_ternary_weight* const* w, 
     bool concat = true;
     for (int i = 0; i < count; i++) {
         if ((st = check_weight(*w[i]))) return st;
-        concat = concat && (w[i]->out_features % 16 == 0) && (w[i]->in_features == w[0]->in_features);
+        concat = concat && (w[i]->out_features % packed_row_align() == 0) && (w[i]->in_features == w[0]->in_features);
         total += packed_bytes(w[i]->out_features, w[i]->in_features);
         rows += w[i]->out_features;
     }
@@ -141,7 +141,7 @@ int pack_group(Decoder* D, int count, const tllm_b200_ternary_weight* const* w, 
 // token batches, passes of the streaming GEMV for a few tokens.
 int linear_f16(const PackedW& w, const half* x, half* y, int n_tokens, cudaStream_t stream)
 {
-    if (n_tokens > 6 && gemm_tcgen05_supported(n_tokens, w.rows, w.cols))
+    if (n_tokens > 8 && gemm_tcgen05_supported(n_tokens, w.rows, w.cols))
         return launch_gemm_tcgen05(x, w.p, y, n_tokens, w.rows, w.cols, stream);
     return launch_gemv_packed(w.p, x, y, n_tokens, w.rows, w.cols, stream);
 }

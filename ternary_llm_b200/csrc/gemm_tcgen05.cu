@@ -8,11 +8,12 @@
 // One CTA computes a tile of 128 output features x 256 tokens:
 //   * the weight tile is the MMA's A operand and lives in TENSOR MEMORY: four
 //     expander warps (one thread per feature row = one TMEM lane) read the row's
-//     packed 2-bit codes (packed_layout.cuh) straight from global/L2, expand 128
-//     weights per stage with PRMT (codes -> FP16 high bytes, four weights per
-//     instruction) and one HMUL2 by the group scale per weight pair, and write them
-//     with tcgen05.st.  The expanded weights never touch shared memory, which
-//     leaves its bandwidth to the activation operand;
+//     packed 2-bit codes (packed_layout.cuh) straight from global/L2 and expand 128
+//     weights per stage: the codes c = t + 1 of two weights become the selector of one
+//     PRMT into the byte table {-s, 0, +s} of the group's scale (an integer multiply-add
+//     builds the selector), which yields the FP16 pair directly; tcgen05.st writes
+//     them.  The expanded weights never touch shared memory, which leaves its
+//     bandwidth to the activation operand;
 //   * the activation tile [256 tokens x 128 K] is the B operand in shared memory,
 //     brought by TMA (two 128-byte-swizzled boxes of 64 K per stage, 3 stages);
 //   * one thread issues tcgen05.mma (kind::f16, M=128, N=256, K=16; A from TMEM, B
@@ -55,18 +56,11 @@ struct Cfg {
     static constexpr size_t kSmem = (size_t)kBStages * kStageBytes + 1024;
 };
 
-// PRMT tables: pair code -> FP16 high byte (+1 -> 0x3C, -1 -> 0xBC, 0 -> 0x00).
-// index:            0     1     2     3     4     5     6     7
-// weight a:        +1    +1    +1     0     0    -1    -1    -1
-// weight b:        +1     0    -1    +1    -1    +1     0    -1
-constexpr uint32_t kHiA_lo = 0x003C3C3Cu, kHiA_hi = 0xBCBCBC00u;
-constexpr uint32_t kHiB_lo = 0x3CBC003Cu, kHiB_hi = 0xBC003CBCu;
-
 struct Args {
-    const uint8_t* packed;     // packed weights [ceil(N/16)][K/128] tiles
+    const uint8_t* packed;     // packed weights [ceil(N/64)][K/128] super-tiles
     half* C;                   // [M, N]
     int M, N, K, groups;       // groups = K / 128
-    int nrb;                   // ceil(N / 16)
+    int nrb;                   // ceil(N / 64)
     int* err;
     // split-K (gridDim.z > 1): CTA z contracts stages [z*groups/ks, (z+1)*groups/ks) and writes an
     // FP32 partial tile; the CTA of a tile that arrives last adds the partials in z order.
@@ -155,16 +149,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t lo, uint32_t hi, uint32_t sel)
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(lo), "r"(hi), "r"(sel));
     return r;
-}
-
-// Four FP16 high bytes -> two registers of FP16 pairs {-s,0,+s}.
-__device__ __forceinline__ void expand4(uint32_t hb, __half2 s2, uint32_t& r01, uint32_t& r23)
-{
-    const uint32_t u01 = __byte_perm(hb, 0u, 0x1404), u23 = __byte_perm(hb, 0u, 0x3424);
-    const __half2 v01 = __hmul2(*reinterpret_cast<const __half2*>(&u01), s2);
-    const __half2 v23 = __hmul2(*reinterpret_cast<const __half2*>(&u23), s2);
-    r01 = *reinterpret_cast<const uint32_t*>(&v01);
-    r23 = *reinterpret_cast<const uint32_t*>(&v23);
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16])
@@ -275,31 +259,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
         // ---------------- weight expanders, then epilogue ----------------
         const int row = tid - 128;                       // feature row inside the tile = TMEM lane
         const int n = n0 + row;
-        const int rb = n >> 4, r16 = n & 15;
+        const int rb = n >> 6, r64 = n & 63;             // super-tile row block and row inside it
+        const int f = r64 >> 4, gq = r64 & 7, h = (r64 >> 3) & 1;
         const bool row_valid = rb < a.nrb;               // rows past the matrix expand to zeros
-        const uint8_t* tile0 = a.packed + ((size_t)(row_valid ? rb : 0) * a.groups + it0) * kTileBytes;
-        const int spos = (r16 < 8) ? 2 * r16 : 2 * (r16 - 8) + 1;
+        const uint8_t* tile0 = a.packed + ((size_t)(row_valid ? rb : 0) * a.groups + it0) * kStBytes;
+        // this row's code words of step m, lane t: the pair (column halves j2 = 0, 1) at
+        // word index (m*32 + gq*4 + t)*4 + 2h, i.e. one 64-bit load per (m, t)
+        const int pair0 = (gq * 4) * 2 + h;              // in units of uint2; + m*64 + t*2
+        const int spos = st_scale_index(r64);
+        const int sh = 2 * f;
         const uint32_t lane_base = tmem + ((uint32_t)(row & ~31) << 16);   // this warp's 32 TMEM lanes
 
-        uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
-        half sc = __float2half(0.f);
-        if (row_valid) {
-            c0 = __ldg(reinterpret_cast<const uint4*>(tile0 + r16 * 32));
-            c1 = __ldg(reinterpret_cast<const uint4*>(tile0 + r16 * 32 + 16));
-            sc = __ldg(reinterpret_cast<const half*>(tile0 + kTileCodeBytes) + spos);
-        }
+        uint2 cw[4][4];
+        uint32_t sbits = 0;
+        auto load_stage = [&](const uint8_t* tp) {
+            const uint2* p = reinterpret_cast<const uint2*>(tp) + pair0;
+#pragma unroll
+            for (int m = 0; m < 4; m++)
+#pragma unroll
+                for (int t = 0; t < 4; t++) cw[m][t] = __ldg(p + m * 64 + t * 2);
+            sbits = __half_as_ushort(__ldg(reinterpret_cast<const half*>(tp + kStCodeBytes) + spos));
+        };
+        if (row_valid) load_stage(tile0);
         bool ok = true;
         for (int it = 0; it < nstages; it++) {
             const int sa = it % kAStages;
-            // codes of lanes t = 0..3 of this row: words {step 0|1, step 2|3}
-            const uint32_t w[4][2] = {{c0.x, c0.y}, {c0.z, c0.w}, {c1.x, c1.y}, {c1.z, c1.w}};
-            const __half2 s2 = __half2half2(sc);
-            if (it + 1 < nstages && row_valid) {          // prefetch the next group's codes and scale
-                const uint8_t* tp = tile0 + (size_t)(it + 1) * kTileBytes;
-                c0 = __ldg(reinterpret_cast<const uint4*>(tp + r16 * 32));
-                c1 = __ldg(reinterpret_cast<const uint4*>(tp + r16 * 32 + 16));
-                sc = __ldg(reinterpret_cast<const half*>(tp + kTileCodeBytes) + spos);
-            }
+            // PRMT table of this stage: bytes 0,1 = -s (code 0), 2,3 = 0 (code 1), 4,5 = +s (code 2)
+            const uint32_t tab_lo = row_valid ? (sbits ^ 0x8000u) : 0u, tab_hi = row_valid ? sbits : 0u;
+            uint2 cur[4][4];
+#pragma unroll
+            for (int m = 0; m < 4; m++)
+#pragma unroll
+                for (int t = 0; t < 4; t++) cur[m][t] = cw[m][t];
+            if (it + 1 < nstages && row_valid) load_stage(tile0 + (size_t)(it + 1) * kStBytes);   // prefetch the next group
             if (!mbar_wait(empty_a(sa), ((it / kAStages) & 1) ^ 1, abortp)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_t = lane_base + kAccCols + sa * kAColsPerStage;
@@ -308,11 +300,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
                 uint32_t r[16];
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    const uint32_t word = w[t][m >> 1];
-                    const uint32_t sel = (m & 1) ? (word >> 16) : word;
-                    // weights at K offsets 4t..4t+3 (columns 2t, 2t+1) and 16+4t.. (columns 8+2t, 9+2t)
-                    expand4(prmt(kHiA_lo, kHiA_hi, sel), s2, r[2 * t], r[2 * t + 1]);
-                    expand4(prmt(kHiB_lo, kHiB_hi, sel), s2, r[8 + 2 * t], r[9 + 2 * t]);
+#pragma unroll
+                    for (int j2 = 0; j2 < 2; j2++) {
+                        // four codes (K offsets 16*j2 + 4t .. +3) in the low two bits of each byte
+                        const uint32_t y = ((j2 ? cur[m][t].y : cur[m][t].x) >> sh) & 0x03030303u;
+                        // selector nibbles 2c, 2c+1 per weight: one PRMT makes an FP16 pair {-s,0,+s}
+                        r[8 * j2 + 2 * t] = prmt(tab_lo, tab_hi, y * 0x22u + 0x1010u);
+                        r[8 * j2 + 2 * t + 1] = prmt(tab_lo, tab_hi, (y >> 16) * 0x22u + 0x1010u);
+                    }
                 }
                 tmem_st16(a_t + m * 16, r);
             }
@@ -528,7 +523,7 @@ int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, in
     a.N = N;
     a.K = K;
     a.groups = K / kStageK;
-    a.nrb = (N + 15) / 16;
+    a.nrb = (N + kStRows - 1) / kStRows;
     a.err = err;
     a.ws = nullptr;
     a.counters = nullptr;

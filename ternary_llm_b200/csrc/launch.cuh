@@ -35,40 +35,6 @@ inline void prefer_max_shared(const void* kernel)
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
-#ifdef TLLM_PROFILE_PHASES
-// Timeline probe (never compiled into the shipped library): CTA 0 of every launch appends
-// {kernel id, phase, globaltimer} records to a per-translation-unit buffer.
-static __device__ unsigned long long g_tl_rec[3 * 8192];
-static __device__ unsigned g_tl_n;
-__device__ __forceinline__ void tl_mark(int kernel_id, int phase)
-{
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        const unsigned i = atomicAdd(&g_tl_n, 1u);
-        if (i < 8192) {
-            g_tl_rec[3 * i] = (unsigned long long)kernel_id;
-            g_tl_rec[3 * i + 1] = (unsigned long long)phase;
-            g_tl_rec[3 * i + 2] = t;
-        }
-    }
-}
-#define TL_MARK(id, ph) tl_mark(id, ph)
-#define TL_DUMP(name)                                                                          \
-    extern "C" int name(unsigned long long* out, int max_rec)                                  \
-    {                                                                                          \
-        unsigned n = 0;                                                                        \
-        cudaMemcpyFromSymbol(&n, tllm::g_tl_n, sizeof(n));                                           \
-        if ((int)n > max_rec) n = (unsigned)max_rec;                                           \
-        cudaMemcpyFromSymbol(out, tllm::g_tl_rec, sizeof(unsigned long long) * 3 * n);               \
-        const unsigned zero = 0;                                                               \
-        cudaMemcpyToSymbol(tllm::g_tl_n, &zero, sizeof(zero));                                       \
-        return (int)n;                                                                         \
-    }
-#else
-#define TL_MARK(id, ph)
-#define TL_DUMP(name)
-#endif
 
 template <typename... KArgs, typename... Args>
 int launch_pdl(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

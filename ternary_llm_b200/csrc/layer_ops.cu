@@ -91,11 +91,9 @@ rmsnorm_kernel(const half* __restrict__ input, const half* __restrict__ weight, 
     extern __shared__ __align__(16) float vals[];      // [dim]
     __shared__ float sh[32];
     pdl_launch_dependents();
-    TL_MARK(30, 0);
     const int tid = threadIdx.x;
     const size_t base = (size_t)blockIdx.x * dim;
     pdl_wait();
-    TL_MARK(30, 1);
 
     const half* xin = input + base;
     const half* rin = residual ? residual + base : nullptr;
@@ -365,9 +363,7 @@ __global__ void __launch_bounds__(256)
 embedding_kernel(const half* __restrict__ table, const int* __restrict__ indices, half* __restrict__ out, int dim)
 {
     pdl_launch_dependents();
-    TL_MARK(33, 0);
     pdl_wait();
-    TL_MARK(33, 1);
     const half* src = table + (size_t)indices[blockIdx.x] * dim;
     half* dst = out + (size_t)blockIdx.x * dim;
     if ((dim & 7) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
@@ -398,10 +394,8 @@ fp16_gemv_kernel(const half* __restrict__ w, const half* __restrict__ x, half* _
 {
     extern __shared__ __align__(16) half xs[];
     pdl_launch_dependents();
-    TL_MARK(31, 0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_wait();
-    TL_MARK(31, 1);
     for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = x[i];
     __syncthreads();
     const bool vec = ((cols & 7) == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
@@ -622,9 +616,7 @@ argmax_kernel(const half* __restrict__ logits, int n, int* __restrict__ out, int
     __shared__ int si[kArgmaxThreads / 32];
     __shared__ int s_last;
     pdl_launch_dependents();
-    TL_MARK(32, 0);
     pdl_wait();
-    TL_MARK(32, 1);
     float best = -FLT_MAX;
     int bi = 0x7fffffff;
     for (int i = blockIdx.x * kArgmaxThreads + threadIdx.x; i < n; i += kArgmaxCtas * kArgmaxThreads) {
@@ -697,4 +689,3 @@ int launch_argmax(const half* logits, int n, int* out, int* history, int* step, 
 
 }  // namespace tllm
 
-TL_DUMP(tllm_b200_debug_timeline_layer)

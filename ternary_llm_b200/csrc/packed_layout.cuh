@@ -1,67 +1,60 @@
-// The prepared ("packed") weight layout read by the tensor-core GEMV kernels.
+// The prepared ("packed") weight layout read by the streaming GEMV and the tcgen05 GEMM.
 //
-// A matrix [rows, cols] is cut into tiles of 16 rows x 128 columns (one scale
-// group wide).  Tiles are stored row-block major: tile (rb, g) of a matrix with
-// G = cols/128 groups lives at byte offset (rb*G + g) * kTileBytes.  Rows are
-// padded up to a multiple of 16 with zero weights and zero scales.
+// A matrix [rows, cols] is cut into super-tiles of 64 rows x 128 columns (one scale
+// group wide).  Super-tiles are stored row-block major: super-tile (rb, g) of a matrix
+// with G = cols/128 groups lives at byte offset (rb*G + g) * kStBytes.  Rows are padded
+// up to a multiple of 64 with zero weights and zero scales.
 //
-//   bytes   0..511 : codes.  16 rows x 4 lanes x 2 words.  Word w (0/1) of lane t
-//                    (0..3) of row r sits at (r*4 + t)*8 + w*4.  It holds the 16-bit
-//                    selectors of MMA steps 2w (low half) and 2w+1 (high half).
-//                    The selector of step m has four nibbles n = 0..3; nibble n
-//                    encodes the PAIR of weights at group columns
-//                        ka = 32m + 4t + n      and      kb = 32m + 16 + 4t + n
-//                    as the 4-bit pattern pair_code(ta, tb) below.  That is the
-//                    register layout of the A operand of mma.m16n8k32 (a0 = the
-//                    four `a` weights, a2 = the four `b` weights of a lane), so one
-//                    PRMT per operand register expands four weights.
-//   bytes 512..543 : scales, FP16.  Rows r and r+8 (r = 0..7) are adjacent:
-//                    half[2r] = scale of row r, half[2r+1] = scale of row r+8.
+//   bytes    0..2047 : codes, 512 words of 32 bits.  A weight t in {-1,0,+1} is stored
+//                      as the 2-bit OFFSET CODE c = t + 1 (0, 1, 2; 3 never occurs).
+//                      Word (m, lane, i) at index (m*32 + lane)*4 + i, with
+//                          m    = 0..3   the k32 step of mma.m16n8k32 inside the group
+//                          lane = 0..31  the MMA lane, lane = gq*4 + t
+//                          i    = 0..3   i = 2h + j2: row half h, column half j2
+//                      holds sixteen codes: byte j (0..3), field f (0..3) at bits
+//                      8j + 2f .. 8j + 2f + 1 is the weight at
+//                          row    16f + gq + 8h
+//                          column 32m + 16*j2 + 4t + j              (inside the group)
+//                      So `word & (0x03030303 << 2f)` IS an A-operand register of the MMA
+//                      whose 16 A rows are rows 16f .. 16f+15 of the super-tile (words
+//                      i = 0,1,2,3 are registers a0,a2,a1,a3), as unsigned bytes scaled by
+//                      4^f: one logic instruction per operand register, no shift, no
+//                      table.  The 4^f factor is divided out in FP32 together with the
+//                      scale, and sum(t*x) = sum(c*x) - sum(x).  The two words of one row
+//                      (i = 2h, 2h+1) are adjacent: a thread that expands ONE row, as the
+//                      GEMM's does, reads them with one 64-bit load per (m, t).
+//   bytes 2048..2175 : scales, FP16.  half[gq*8 + f*2 + h] is the scale of row
+//                      16f + gq + 8h: the eight scales an MMA lane needs are 16
+//                      contiguous bytes.
 //
-// pair_code: the eight pairs other than (0,0) take patterns 0..7 in the order
-// (+,+) (+,0) (+,-) (0,+) (0,-) (-,+) (-,0) (-,-); the pair (0,0) is pattern 8.
-// A PRMT selector nibble uses bits 0..2 as a byte index into an 8-byte table and
-// bit 3 as "replicate the sign bit of the selected byte"; entry 0 of both tables
-// is +1 (sign bit clear), so pattern 8 yields 0x00 for both weights.
-//
-// The layout keeps 2 bits per weight and all FP16 scales: it is exactly as large
-// as the three reference arrays for 16-row-aligned matrices, and it is lossless
-// for canonical masks (sign bit set only where the nonzero bit is set), which is
-// all the reference's packer emits (ternarize/pack.py:135-138).
+// The layout keeps 2 bits per weight and all FP16 scales: it is exactly as large as
+// the three reference arrays for matrices whose row count is a multiple of 64, and it
+// is lossless for canonical masks (sign bit set only where the nonzero bit is set),
+// which is all the reference's packer emits (ternarize/pack.py:135-138).
 #pragma once
 #include <cstdint>
 
 namespace tllm {
 
-constexpr int kTileRows = 16;
-constexpr int kTileCodeBytes = 512;
-constexpr int kTileBytes = 544;
+constexpr int kStRows = 64;
+constexpr int kStCodeBytes = 2048;
+constexpr int kStScaleBytes = 128;
+constexpr int kStBytes = kStCodeBytes + kStScaleBytes;   // 2176
 
-// PRMT tables (bytes 0..3 in the low word, 4..7 in the high word), INT8 operands.
-// index:            0     1     2     3     4     5     6     7
-// weight a:        +1    +1    +1     0     0    -1    -1    -1
-// weight b:        +1     0    -1    +1    -1    +1     0    -1
-constexpr uint32_t kTabA_lo = 0x00010101u, kTabA_hi = 0xFFFFFF00u;
-constexpr uint32_t kTabB_lo = 0x01FF0001u, kTabB_hi = 0xFF0001FFu;
-
-// (ta, tb) in {-1,0,+1}^2 -> 4-bit pattern.
-__host__ __device__ inline uint32_t pair_code(int ta, int tb)
+// Weight (r64, c) of a super-tile, r64 = 0..63, c = 0..127: index of its code word and
+// the bit position of its 2-bit code inside that word.
+__host__ __device__ inline void st_locate(int r64, int c, int& word, int& shift)
 {
-    if (ta == 0 && tb == 0) return 8u;
-    // rows of the table above: a = +1 -> 0..2, a = 0 -> 3..4, a = -1 -> 5..7
-    if (ta > 0) return (uint32_t)(1 - tb);            // +1:0, 0:1, -1:2
-    if (ta == 0) return tb > 0 ? 3u : 4u;
-    return (uint32_t)(6 - tb);                        // +1:5, 0:6, -1:7
+    const int f = r64 >> 4, gq = r64 & 7, h = (r64 >> 3) & 1;
+    const int m = c >> 5, j2 = (c >> 4) & 1, t = (c >> 2) & 3, j = c & 3;
+    word = (m * 32 + gq * 4 + t) * 4 + 2 * h + j2;
+    shift = 8 * j + 2 * f;
 }
 
-// 4-bit pattern -> (ta, tb); the inverse of pair_code (patterns 9..15 never occur).
-__host__ __device__ inline void pair_decode(uint32_t p, int& ta, int& tb)
+// Index of row r64's scale among the 64 FP16 scales of a super-tile.
+__host__ __device__ inline int st_scale_index(int r64)
 {
-    const int8_t a[9] = {1, 1, 1, 0, 0, -1, -1, -1, 0};
-    const int8_t b[9] = {1, 0, -1, 1, -1, 1, 0, -1, 0};
-    const uint32_t i = p > 8u ? 8u : p;
-    ta = a[i];
-    tb = b[i];
+    return (r64 & 7) * 8 + (r64 >> 4) * 2 + ((r64 >> 3) & 1);
 }
 
 }  // namespace tllm

@@ -266,10 +266,11 @@ class _PinnedStager:
         host = self.bufs[i][:n]
         np.copyto(host.numpy().view(a.dtype).reshape(a.shape), a)
         dt = {"uint32": torch.int32, "float16": torch.float16}[a.dtype.name]
-        out = torch.empty(a.shape, dtype=dt, device=self.device)
-        out.view(torch.uint8).reshape(-1).copy_(host, non_blocking=True)
-        self.events[i] = torch.cuda.Event()
-        self.events[i].record()
+        with torch.cuda.device(self.device):      # the event must belong to the target device's stream
+            out = torch.empty(a.shape, dtype=dt, device=self.device)
+            out.view(torch.uint8).reshape(-1).copy_(host, non_blocking=True)
+            self.events[i] = torch.cuda.Event()
+            self.events[i].record()
         return out
 
 
@@ -309,22 +310,25 @@ def load_projections(path: str, device, register: bool = False, rank: int = 0, w
             raise ValueError(f"{what}: the prepared matrix does not unpack to the arrays of the file")
 
     out = []
-    for li, layer in enumerate(shards):
-        d = {}
-        todo = list(PROJ_NAMES)
-        if grouped:
-            for names in TP_GROUPS:
-                srcs = [device_arrays(layer[n]) for n in names]
-                for n, w, src in zip(names, ops.prepare_group(srcs), srcs):
-                    d[n] = w
-                    if verify:
-                        check(w, src, f"layer {li} {n}")
-                    todo.remove(n)
-        for name in todo:
-            src = device_arrays(layer[name])
-            d[name] = ops.PreparedWeight(*src, register=register, keep_source=register)
-            if verify:
-                check(d[name], src, f"layer {li} {name}")
-        out.append(d)
+    # the library's kernels run on the CURRENT device: make the target device current for the
+    # repack launches (and for the staging copies' events)
+    with torch.cuda.device(torch.device(device)):
+        for li, layer in enumerate(shards):
+            d = {}
+            todo = list(PROJ_NAMES)
+            if grouped:
+                for names in TP_GROUPS:
+                    srcs = [device_arrays(layer[n]) for n in names]
+                    for n, w, src in zip(names, ops.prepare_group(srcs), srcs):
+                        d[n] = w
+                        if verify:
+                            check(w, src, f"layer {li} {n}")
+                        todo.remove(n)
+            for name in todo:
+                src = device_arrays(layer[name])
+                d[name] = ops.PreparedWeight(*src, register=register, keep_source=register)
+                if verify:
+                    check(d[name], src, f"layer {li} {name}")
+            out.append(d)
     torch.cuda.synchronize(torch.device(device))
     return m.config, out

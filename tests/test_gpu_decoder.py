@@ -12,7 +12,7 @@ import torch
 import ternary_llm_b200 as tl
 from oracle import cpu
 from oracle import layer_oracle as LO
-from tests import run_engine_e2e as e2e
+from tests import _engine_e2e as e2e
 from ternary_llm_b200 import tllm_format as tf
 
 pytestmark = pytest.mark.gpu

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from oracle import cpu
-from tests import run_engine_e2e as e2e
+from tests import _engine_e2e as e2e
 from ternary_llm_b200 import tllm_format as tf
 
 pytestmark = pytest.mark.gpu

@@ -1,0 +1,170 @@
+"""GPU parity at the sizes the benchmark definition names: the LLaMA-3-8B projection shapes
+at batch 4 and 16, the prefill GEMM at the gate/up and down shapes for 128 / 512 / 2048
+tokens, and the per-rank shapes of the LLaMA-70B tensor-parallel split on one GPU.
+
+Weights are drawn on the device (seeded); the oracle (float64, the 2e-3 * sum|scale*t*x|
+bound plus half an FP16 ulp) is evaluated on a sample of output rows that always holds the
+first and the last 64-row block and the rows either side of every 1/37 of the matrix, which
+is where a row block changes hands between CTAs.  Every output, sampled or not, must be
+finite and -- a size-independent property -- doubling the activations must double every
+output exactly.
+"""
+import numpy as np
+import pytest
+import torch
+
+import ternary_llm_b200 as tl
+from ternary_llm_b200 import synth
+from tests._util import assert_within, exact_and_bound
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+SHAPES_8B = {"q/o": (4096, 4096), "k/v": (1024, 4096), "gate/up": (14336, 4096), "down": (4096, 14336)}
+
+
+def _half_ulp(y64):
+    a = np.maximum(np.abs(y64), 2.0 ** -14)
+    return 0.5 * 2.0 ** (np.floor(np.log2(a)) - 10)
+
+
+def _sample_rows(n, count=384, seed=0):
+    rows = set(range(min(64, n))) | set(range(max(0, n - 64), n))
+    for i in range(1, 37):                      # neighbourhoods of evenly spread cut points
+        c = n * i // 37
+        rows |= {r for r in (c - 1, c, c + 1) if 0 <= r < n}
+    rng = np.random.default_rng(seed)
+    rows |= set(int(r) for r in rng.integers(0, n, count))
+    return np.array(sorted(rows))
+
+
+def _weights(n, k, seed):
+    torch.cuda.set_device(0)
+    nz, sg, sc = synth.random_ternary_weight(n, k, seed=seed, device=torch.device(DEV))
+    w = tl.PreparedWeight(nz, sg, sc, n, k, register=False)
+    return nz, sg, sc, w
+
+
+def _host_rows(nz, sg, sc, rows):
+    idx = torch.from_numpy(rows).to(DEV)
+    return (nz[idx].cpu().numpy().view(np.uint32), sg[idx].cpu().numpy().view(np.uint32), sc[idx].cpu().numpy())
+
+
+def _check_rows(y_gpu, nz, sg, sc, rows, x, what):
+    """y_gpu [B, N] float16 numpy; x [B, K] float16 numpy."""
+    hnz, hsg, hsc = _host_rows(nz, sg, sc, rows)
+    y64, bound = exact_and_bound(hnz, hsg, hsc, x)
+    assert np.isfinite(y_gpu).all(), f"{what}: non-finite outputs"
+    return assert_within(y_gpu[:, rows], y64, bound, what, slack=_half_ulp(y64))
+
+
+@pytest.mark.parametrize("batch", [4, 16])
+@pytest.mark.parametrize("name", list(SHAPES_8B))
+def test_gemv_batched_at_8b_shapes(name, batch):
+    n, k = SHAPES_8B[name]
+    nz, sg, sc, w = _weights(n, k, seed=1000 + n + k)
+    x = np.random.default_rng(batch + n).standard_normal((batch, k)).astype(np.float16)
+    dx = torch.from_numpy(x).to(DEV)
+    y = torch.full((batch, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, dx, y, batch)
+    y2 = torch.full((batch, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, (dx.float() * 2).half(), y2, batch)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    _check_rows(y.cpu().numpy(), nz, sg, sc, _sample_rows(n, seed=batch), x, f"gemv {name} batch {batch}")
+    assert torch.equal(y2.float(), y.float() * 2), "W(2x) != 2 W(x)"
+
+
+GEMM_CASES = [(m, s) for s in ("gate/up", "down") for m in (128, 512, 2048)] + [(2048, "k/v"), (2048, "q/o")]
+
+
+@pytest.mark.parametrize("m,name", GEMM_CASES)
+def test_gemm_at_8b_shapes(m, name):
+    """The tcgen05 GEMM at the prefill sizes of the benchmark definition (k/v at 2048 tokens
+    takes the split-K path), sampled tokens x sampled features against the oracle."""
+    n, k = SHAPES_8B[name]
+    nz, sg, sc, w = _weights(n, k, seed=2000 + n + k)
+    a = torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(m)).half()
+    c = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemm_packed(a, w, c, m)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    assert bool(torch.isfinite(c).all())
+    toks = np.unique(np.concatenate([[0, m - 1, m // 2, 255 % m, 256 % m],
+                                     np.random.default_rng(m).integers(0, m, 6)]))
+    rows = _sample_rows(n, count=256, seed=m)
+    x = a[torch.from_numpy(toks).to(DEV)].cpu().numpy()
+    cg = c[torch.from_numpy(toks).to(DEV)].cpu().numpy()
+    _check_rows(cg, nz, sg, sc, rows, x, f"gemm M={m} {name}")
+
+
+def _tp_shapes():
+    out = [(8192, 8192), (8192, 28672), (28672, 8192)]
+    for tp in (2, 4, 8):
+        out += [(28672 // tp, 8192), (8192, 28672 // tp), (8192, 8192 // tp), (8192 // tp, 8192), (1024 // tp, 8192)]
+    return sorted(set(out))
+
+
+@pytest.mark.parametrize("n,k", _tp_shapes())
+def test_gemv_at_70b_shard_shapes(n, k):
+    """Every matrix shape one rank of the LLaMA-70B tensor-parallel split streams (tp = 2, 4,
+    8), and the unsharded shapes, batch 1, FP16 and INT8 activations."""
+    nz, sg, sc, w = _weights(n, k, seed=3000 + n + k)
+    x = np.random.default_rng(n + k).standard_normal((1, k)).astype(np.float16)
+    dx = torch.from_numpy(x).to(DEV)
+    y = torch.full((1, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, dx, y, 1)
+    q = torch.zeros(k, dtype=torch.int8, device=DEV)
+    scale = torch.zeros(1, dtype=torch.float32, device=DEV)
+    tl.quantize_absmax_int8(dx[0], q, scale, k)
+    yi = torch.full((n,), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_int8_packed(w, q, float(scale.item()), yi)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    rows = _sample_rows(n, seed=k)
+    _check_rows(y.cpu().numpy(), nz, sg, sc, rows, x, f"gemv {n}x{k}")
+    xq = (q.cpu().numpy().astype(np.float64) * float(scale.item()))[None, :]
+    hnz, hsg, hsc = _host_rows(nz, sg, sc, rows)
+    y64, bound = exact_and_bound(hnz, hsg, hsc, xq)
+    got = yi.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert_within(got[None, rows], y64, bound, f"gemv int8 {n}x{k}", slack=_half_ulp(y64))
+
+
+def test_gemv_config0_shape():
+    """The single-GEMV configuration: K = 2048, N = 8192 (the 1B up-projection)."""
+    n, k = 8192, 2048
+    nz, sg, sc, w = _weights(n, k, seed=7)
+    x = np.random.default_rng(7).standard_normal((1, k)).astype(np.float16)
+    y = torch.full((1, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, torch.from_numpy(x).to(DEV), y, 1)
+    torch.cuda.synchronize()
+    _check_rows(y.cpu().numpy(), nz, sg, sc, np.arange(n), x, "config 0")
+
+
+def test_non_finite_activations_reach_the_output():
+    """FP32 accumulation of x, as the reference does it, carries a NaN or an infinity into
+    the result; the block-fixed-point staging must not hide one.  Here a scale group that
+    holds a non-finite activation makes every output NaN (the dequantise-then-multiply
+    oracle gives NaN or an infinity in those outputs); a vector without one is untouched."""
+    n, k = 192, 512
+    nz, sg, sc, w = _weights(n, k, seed=9)
+    x = np.random.default_rng(9).standard_normal((3, k)).astype(np.float16)
+    x[0, 130] = np.nan
+    x[1, 300] = np.inf
+    dx = torch.from_numpy(x).to(DEV)
+    for batch in (1, 2, 3):
+        y = torch.zeros(batch, n, dtype=torch.float16, device=DEV)
+        tl.ternary_gemv_packed(w, dx[:batch].contiguous(), y, batch)
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(y[0]).all())
+        if batch > 1:
+            assert bool(torch.isnan(y[1]).all())
+        if batch > 2:
+            rows = np.arange(n)
+            _check_rows(y.cpu().numpy()[2:3], nz, sg, sc, rows, x[2:3], "finite vector beside non-finite ones")
+    # one vector alone with the non-finite value: same
+    y = torch.zeros(1, n, dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, dx[1:2].contiguous(), y, 1)
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(y).all())

@@ -135,6 +135,72 @@ def test_ops_refuse_cpu_tensors():
         tl.ternary_gemv(a, a, s, x, y, 16, 128)
 
 
+class _FakeCuda:
+    """Stands in for a CUDA tensor in the wrappers' checks (no GPU on the build machine): the
+    checks read only these attributes."""
+
+    def __init__(self, numel, dtype, index=0, contiguous=True):
+        import torch
+        self._n, self.dtype, self.is_cuda = numel, dtype, True
+        self.device = torch.device("cuda", index)
+        self._c = contiguous
+
+    def numel(self):
+        return self._n
+
+    def is_contiguous(self):
+        return self._c
+
+    def data_ptr(self):
+        return 0x1000
+
+
+def test_wrappers_refuse_short_tensors_and_foreign_devices(monkeypatch):
+    """Nothing may be launched on a tensor that is too small for the stated shape or that lives
+    on another GPU than the current one: the kernels trust rows/cols and run on the current
+    device, so either mistake would make them touch memory that is not theirs."""
+    import torch
+    from ternary_llm_b200 import ops
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+
+    class NoCall:
+        def __getattr__(self, name):
+            def fn(*a):
+                raise AssertionError(f"{name} was called although an argument check should have failed")
+            return fn
+    monkeypatch.setattr(_lib, "lib", lambda: NoCall())
+    n, k = 64, 256
+    i32, f16, i8 = torch.int32, torch.float16, torch.int8
+    good = lambda: (_FakeCuda(n * k // 32, i32), _FakeCuda(n * k // 32, i32), _FakeCuda(n * k // 128, f16))
+    # short mask / scale / input / output arrays
+    for bad in range(3):
+        w = list(good())
+        w[bad] = _FakeCuda(w[bad].numel() - 1, w[bad].dtype)
+        with pytest.raises(ValueError, match="holds"):
+            tl.ternary_gemv(*w, _FakeCuda(k, f16), _FakeCuda(n, f16), n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.ternary_gemv(*good(), _FakeCuda(k - 1, f16), _FakeCuda(n, f16), n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.ternary_gemv(*good(), _FakeCuda(k, f16), _FakeCuda(n - 1, f16), n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.ternary_gemv_batched(*good(), _FakeCuda(3 * k, f16), _FakeCuda(4 * n, f16), 4, n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.ternary_gemv_int8(*good(), _FakeCuda(k - 16, i8), 1.0, _FakeCuda(n, f16), n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.ternary_gemm(_FakeCuda(2 * k, f16), *good(), _FakeCuda(3 * n, f16), 3, n, k)
+    with pytest.raises(ValueError, match="holds"):
+        tl.quantize_absmax_int8(_FakeCuda(k, f16), _FakeCuda(k, i8), _FakeCuda(0, torch.float32), k)
+    # a tensor on another device than the current one
+    with pytest.raises(ValueError, match="current device"):
+        tl.ternary_gemv(*good(), _FakeCuda(k, f16, index=1), _FakeCuda(n, f16), n, k)
+    with pytest.raises(ValueError, match="current device"):
+        ops.PreparedWeight(_FakeCuda(n * k // 32, i32, index=1), _FakeCuda(n * k // 32, i32, index=1),
+                           _FakeCuda(n * k // 128, f16, index=1), n, k)
+    # shapes the kernels do not take
+    with pytest.raises(ValueError, match="multiple of 128"):
+        tl.ternary_gemv(*good(), _FakeCuda(k, f16), _FakeCuda(n, f16), n, 200)
+
+
 def test_torch_synth_matches_numpy_packer():
     import torch
     from ternary_llm_b200 import synth

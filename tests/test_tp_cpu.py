@@ -76,4 +76,4 @@ def test_bench_tp_shapes_cover_the_full_matrices():
         assert shapes["gate"] == (28672 // tp, 8192) and shapes["down"] == (8192, 28672 // tp)
         assert shapes["k"] == (1024 // tp, 8192)
         for _, r, c in bench.tp_shapes(tp):
-            assert r % 16 == 0 and c % 128 == 0
+            assert r % 64 == 0 and c % 128 == 0
