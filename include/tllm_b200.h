@@ -200,16 +200,28 @@ int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, 
                                     int rows_max, void* stream);
 
 /*
+ * Time stamps of the fused all-reduce, for finding out where a tensor-parallel step spends
+ * its time.  While a buffer is set for the current device, CTA 0 of every
+ * tllm_b200_gemv_packed_allreduce launch on it writes a record of eight 64-bit words to
+ * buffer[(e % records) * 8 ..], e being the launch number: the GPU's nanosecond timer at
+ * {kernel entry, end of the stream-order wait, partial sums ready, peer stores issued, all
+ * ranks' words seen and summed}, then e, then two unused words.  buffer: device memory of
+ * records * 64 bytes, owned by the caller; NULL switches the stamps off (the default).  Costs
+ * a few instructions per launch.  No counterpart in the reference.
+ */
+int tllm_b200_allreduce_trace(void* buffer, int records);
+
+/*
  * tllm_b200_gemv_packed for one FP16 vector, for callers that cannot let a library
  * allocate device memory (a server that owns all of HBM through its own arena, a
  * real-time loop, a host that audits allocations up front).  It has no counterpart
  * in the reference.  Nothing is allocated, by this call or any routine it uses: the
- * split-K scratch is a fixed 84 KB array inside the library image, present on every
+ * split-K scratch is a fixed 160 KB array inside the library image, present on every
  * GPU that loads the library until the process exits.
  * Limits: rows <= 65536 (TLLM_ERR_SIZE beyond), cols as for tllm_b200_gemv_packed.
  * The first call on a device resolves the array's device address and configures the
  * kernel; make that first call before any stream capture.  All calls share the one
- * array and it keeps the last call's contents (the arrival counters are cleared on
+ * array and it keeps the last call's contents (its records are cleared on
  * `stream` before each launch): calls whose kernels overlap on the GPU, for example
  * from two streams, race with each other -- serialise them.
  */

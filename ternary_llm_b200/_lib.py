@@ -9,7 +9,8 @@ import ctypes
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libtllm_b200.so")
+# TLLM_B200_LIB names another build of the library to load (the diagnostic one, see build.py)
+LIB_PATH = os.environ.get("TLLM_B200_LIB") or os.path.join(PKG, "libtllm_b200.so")
 
 _vp = ctypes.c_void_p
 _int = ctypes.c_int
@@ -36,6 +37,7 @@ SIGNATURES = {
     "tllm_b200_gemv_packed_noalloc": (_int, [_vp] * 3 + [_int] * 2 + [_vp]),
     "tllm_b200_gemv_packed_noalloc_status": (_int, [_vp]),
     "tllm_b200_gemv_packed_allreduce": (_int, [_vp] * 3 + [_int] * 4 + [_vp] * 2 + [_int, _vp]),
+    "tllm_b200_allreduce_trace": (_int, [_vp, _int]),
     "tllm_b200_gemv_packed_multi": (_int, [_int, _vp, _vp, _vp, _int, _vp, _vp]),
     # include/tllm_b200_layer.h
     "tllm_b200_rmsnorm": (_int, [_vp] * 5 + [_int, _int, ctypes.c_float, _vp]),

@@ -1,6 +1,11 @@
 """Compile libtllm_b200.so in-tree with nvcc for sm_100a.
 
-    python -m ternary_llm_b200.build [--force]
+    python -m ternary_llm_b200.build [--force] [-v] [--timeline]
+
+--timeline builds a second, diagnostic library, libtllm_b200_timeline.so, with
+-DTLLM_TIMELINE: its GEMV kernels record time stamps of their phases (see
+csrc/gemv_mma.cu) and it exports tllm_b200_timeline_read.  Point TLLM_B200_LIB at it to
+load it instead of the regular library.
 
 The library is a single shared object built from every .cu file under csrc/.
 nvcc cross-compiles without a GPU, so this runs on a CPU-only build machine.
@@ -35,17 +40,18 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, timeline: bool = False) -> str:
+    out = os.path.join(PKG, "libtllm_b200_timeline.so") if timeline else LIB
+    if not timeline and not force and not _stale():
         return LIB
-    cmd = ["nvcc"] + NVCC_FLAGS + ["-I" + os.path.join(ROOT, "include"),
-                                   "-I" + os.path.join(PKG, "csrc"), "-o", LIB] + sources()
+    cmd = ["nvcc"] + NVCC_FLAGS + (["-DTLLM_TIMELINE"] if timeline else []) + \
+        ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(PKG, "csrc"), "-o", out] + sources()
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     subprocess.check_call(cmd)
-    return LIB
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, timeline="--timeline" in sys.argv))

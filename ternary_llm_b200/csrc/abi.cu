@@ -271,6 +271,12 @@ int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, 
                                         peer_recv, epoch_local, rows_max, (cudaStream_t)stream);
 }
 
+int tllm_b200_allreduce_trace(void* buffer, int records)
+{
+    if (buffer && misaligned(buffer, 8)) return fail(TLLM_ERR_ALIGN, "trace buffer must be 8-byte aligned");
+    return allreduce_set_trace(buffer, records);
+}
+
 int tllm_b200_gemv_packed_noalloc(const void* packed, const void* x, void* y, int rows, int cols, void* stream)
 {
     int st = check_packed_call(packed, x, y, rows, cols);

@@ -51,6 +51,7 @@ int* device_error_flag();
 int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, int rows, int cols, int rank,
                                  int world, void* const* peer_recv, void* epoch_local, int rows_max,
                                  cudaStream_t stream);
+int allreduce_set_trace(void* buffer, int records);
 int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
                              const half* x, cudaStream_t stream);
 int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half* const* y, const int* rows,

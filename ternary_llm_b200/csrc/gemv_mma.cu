@@ -25,12 +25,18 @@
 // group, 2176 bytes; row-block major).  They are dealt to CTAs (one per SM) and, inside
 // a CTA, to 16 warps in contiguous, equal ranges, so K is split wherever rows alone
 // would not balance 148 SMs.  Weights arrive through ONE ring of R slots per CTA
-// (cp.async.bulk + one mbarrier per slot, a super-tile per slot): the j-th super-tile
+// (16-byte cp.async copies issued by all lanes of a warp, completion counted on one
+// mbarrier per slot, a super-tile per slot -- measured on this part, a ring fed by
+// cp.async.bulk tops out near 4 TB/s over the whole GPU whatever its depth, while
+// per-thread loads reach the full HBM rate): the j-th super-tile
 // of warp w has sequence number u = 16j + w and uses slot u mod R, so the ring is
 // shared evenly whatever R is, R is simply what the shared-memory budget allows (two
 // CTAs per SM: one computing, the next launch prefetching), and the first R are
 // requested at kernel start.  The warp that finishes sequence number u refills its
-// slot with u + R.  Partial sums of a 64-row block are combined in a fixed order:
+// slot with u + R and publishes the slot's new use number in shared memory first: the
+// consumer of u + R (another warp) looks at that number before it waits on the slot's
+// mbarrier, because a parity wait on a barrier that is still one phase behind would
+// return at once.  Partial sums of a 64-row block are combined in a fixed order:
 // first over the warps of a CTA, then, for a block that spans several CTAs, by
 // whichever CTA arrives last, which adds the CTAs' records in CTA order.  Results
 // therefore do not depend on timing.
@@ -64,7 +70,14 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 #define TLLM_GEMV_CORESIDENT_BYTES (112 * 1024)
 #endif
 constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
-constexpr size_t kMaxSmemBytes = 227 * 1024;
+constexpr size_t kMaxSmemBytes = 226 * 1024;      // dynamic part; the kernel also has a few static bytes
+// L2 prefetch at kernel start of what a warp will stream beyond its first ring fill, in bytes
+// per warp (0 = off).  The fill itself is bounded by shared memory; this lets the HBM stream
+// of a launch go on into the 126 MB L2 while the launch still waits for the kernel before it.
+#ifndef TLLM_GEMV_L2_PREFETCH_BYTES
+#define TLLM_GEMV_L2_PREFETCH_BYTES 0
+#endif
+constexpr int kL2PrefetchSt = TLLM_GEMV_L2_PREFETCH_BYTES / kStBytes;
 
 // kI8Norm / kI8Silu / kI8Quant: INT8 arithmetic like kI8, but the activation vector is
 // produced inside the kernel's staging phase from FP16 inputs (stage_x_fused below).
@@ -99,17 +112,26 @@ struct GemvArgs {
     int late_release;       // 1: the next kernel in the stream is released after this kernel's own dependency
                             //    wait instead of at its start (see release_rule)
     int ring_slots;         // R
-    float* ws;              // [gridDim.x][2][ws_stride / 2] partial records of this ticket
-    int ws_stride;          // floats per CTA in ws (two records)
-    int* counters;          // [row blocks] arrival counters of this ticket (zero between launches)
+    int l2_prefetch;        // 1: a warp asks for (part of) its super-tiles beyond the first ring fill to be
+                            //    brought into L2 at kernel start
+    int x_local;            // FP16 modes, CTAs with fewer super-tiles than a row has groups: a CTA stages only
+                            // the groups it walks (a cyclic run starting at its first super-tile's group)
+    uint2* ws;              // [gridDim.x][2][ws_stride / 2] partial records {value, flag} of this ticket,
+                            // all zero between launches
+    int ws_stride;          // words per CTA in ws (two records)
     int* err;               // device error flag (0 = none)
     // shared memory carve-up (byte offsets); the staged activations start at 0
-    int off_xcst, off_part, off_ring, off_bar;
+    int off_xcst, off_part, off_ring, off_bar, off_gen;
     // Fused all-reduce over peer memory (row-parallel shards of a tensor-parallel layer);
     // ar_world == 0 switches it off.  Every rank runs the same launch on its own shard.
     int ar_world, ar_rank, ar_rows_max;
     uint2* ar_recv[kMaxPeers];        // rank d's receive buffer  {value, launch number} [2][world][ar_rows_max]
     unsigned* ar_epoch;               // this rank's launch counters, uint [kMaxCtas]
+    // Optional time stamps of the fused all-reduce (nullptr = off): CTA 0 writes, for launch
+    // number e, the %globaltimer values {kernel entry, dependency wait over, partial sums ready,
+    // peer stores issued, all ranks' words seen} to ar_trace[(e % ar_trace_cap) * 8 ..].
+    unsigned long long* ar_trace;
+    int ar_trace_cap;
 };
 
 // When a launch releases the next kernel of the stream.  Released at its start, the next
@@ -127,16 +149,35 @@ static inline int release_rule(int rows, int cols)
     return bytes <= (size_t)TLLM_LATE_RELEASE_BYTES ? 1 : 0;
 }
 
+// Diagnostic build only (python -m ternary_llm_b200.build --timeline, which defines
+// TLLM_TIMELINE and writes libtllm_b200_timeline.so): thread 0 of every CTA of every GEMV launch
+// records the GPU's nanosecond timer at seven points -- kernel entry, first ring fill issued,
+// stream-order wait over, activations staged, last super-tile done, partial sums exchanged
+// inside the CTA, outputs written -- into a ring of the last 8 launches, read back by
+// tllm_b200_timeline_read.  The shipped library contains none of this.
+#ifdef TLLM_TIMELINE
+__device__ unsigned long long g_tl[8][kMaxCtas][8];
+__device__ unsigned g_tl_cnt[kMaxCtas];
+#define TL_BEGIN() unsigned tl_slot = 0; if (threadIdx.x == 0) tl_slot = g_tl_cnt[blockIdx.x]++ & 7u
+#define TL(k) do { if (threadIdx.x == 0) g_tl[tl_slot][blockIdx.x][k] = globaltimer(); } while (0)
+#else
+#define TL_BEGIN()
+#define TL(k)
+#endif
+
 // ---- PTX helpers ------------------------------------------------------------
+__device__ __forceinline__ unsigned long long globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 {
@@ -153,11 +194,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
         if (mbar_try(bar, parity)) return true;
     return false;
 }
-// Bulk copy global -> this CTA's shared memory, completion counted on `bar`.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+// One super-tile global -> shared by the 32 lanes of a warp: 136 copies of 16 bytes (lanes 0..7
+// issue a fifth one), then each lane makes the slot's mbarrier count its copies: the barrier
+// (initialised to 32 arrivals) completes its phase when every lane's copies have landed.
+__device__ __forceinline__ void fill_slot(uint32_t dst, const uint8_t* src, uint32_t bar, int lane)
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                     ::"r"(dst + (uint32_t)(i * 32 + lane) * 16u), "l"(src + (size_t)(i * 32 + lane) * 16) : "memory");
+    if (lane < kStBytes / 16 - 128)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                     ::"r"(dst + (uint32_t)(128 + lane) * 16u), "l"(src + (size_t)(128 + lane) * 16) : "memory");
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // D = A.B (+ D unless FIRST), A unsigned bytes (offset codes), B signed bytes.  The zero
@@ -214,17 +263,19 @@ __device__ __forceinline__ void quad_digits(uint32_t q0, uint32_t q1, uint32_t q
 
 // Each thread converts 8 consecutive activations (one 128-bit load); the 16 lanes of a
 // half-warp cover one scale group and agree on its exponent and sums with shuffles.
+// The groups staged are the cyclic run g0, g0+1, ... (mod groups) of length gcount; staged
+// group number i of that run is stored at index i (gcount == groups, g0 == 0: all of them).
 template <int NB, int NV>
 __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols, int groups, int batch,
-                                            uint32_t* xdig, uint4* xcst, int tid)
+                                            uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount)
 {
     constexpr int NVT = NB * NV;
-    const int per_vec = cols >> 3;                 // 8-element items per vector (multiple of 16)
+    const int per_vec = gcount << 4;               // 8-element items per vector (16 per group)
     const int items = per_vec * batch;
     const int l16 = tid & 15;
     // vectors of the last block that do not exist: their constants are zero, so whatever the
     // MMA makes of their (unwritten) digit columns never reaches a finite-times-NaN product
-    for (int i = tid; i < groups * (NVT - batch); i += kThreads) {
+    for (int i = tid; i < gcount * (NVT - batch); i += kThreads) {
         const int g = i / (NVT - batch), v = batch + i % (NVT - batch);
         xcst[g * NVT + v] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -233,9 +284,11 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
         const bool valid = item < items;           // uniform per half-warp
         const int ic = valid ? item : 0;
         const int b = (int)((unsigned)ic / (unsigned)per_vec);
-        const int e8 = ic - b * per_vec;           // item index inside the vector
-        const int g = e8 >> 4;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + e8);
+        const int el = ic - b * per_vec;           // item index inside the staged run
+        const int g = el >> 4;                     // staged group number
+        int gg = g0 + g;                           // its group in the vector
+        if (gg >= groups) gg -= groups;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + (el & 15));
         float f[8];
         {
             const float2 f0 = __half22float2(*reinterpret_cast<const half2*>(&raw.x));
@@ -474,7 +527,7 @@ __device__ __forceinline__ half* out_ptr(const GemvArgs& a, int b, int r)
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
-template <int MODE, int NB, int NV>
+template <int MODE, int NB, int NV, bool AR>
 __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs a)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -486,6 +539,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     if (!a.late_release) asm volatile("griddepcontrol.launch_dependents;");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the fused all-reduce is an instantiation of its own (one FP16 vector only)
+    constexpr bool kAr = AR;
+    static_assert(!AR || (MODE == kF16 && NB == 1 && NV == 1), "the fused all-reduce carries one FP16 vector");
+    __shared__ unsigned long long ts[5];     // time stamps of a traced all-reduce launch (thread 0 of CTA 0)
+    const bool tracing = kAr && (a.ar_trace != nullptr) && blockIdx.x == 0 && tid == 0;
+    if (tracing) ts[0] = globaltimer();
+    TL_BEGIN();
+    TL(0);
     const int G = a.groups, R = a.ring_slots;
     const int per = a.aligned ? G : 1;                                     // super-tiles per partition item
     const int t0 = part_start(blockIdx.x, a.part_q, a.part_r) * per;      // first super-tile of this CTA
@@ -500,25 +561,42 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     const uint32_t ring = smem_addr(smem + a.off_ring);
     const uint8_t* ring_p = smem + a.off_ring;
     const uint32_t bar = smem_addr(smem + a.off_bar);
+    volatile uint32_t* gen = reinterpret_cast<volatile uint32_t*>(smem + a.off_gen);   // use number of each slot
 
     // ---- this warp's super-tile range and the first ring fill ---------------------
     const int w0 = t0 + warp_start(warp, n), w1 = t0 + warp_start(warp + 1, n);
     const int nw = w1 - w0;                                  // may be 0 for tiny problems
     if (lane == 0) {
-        for (int s = warp; s < R; s += kWarps) mbar_init(bar + s * 8, 1);
+        for (int s = warp; s < R; s += kWarps) {
+            mbar_init(bar + s * 8, 32);
+            gen[s] = 0u;
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    {
         // sequence numbers 16j + warp < R go to slots of the same number
-        for (int j = 0, s = warp; s < R && j < nw; j++, s += kWarps) {
-            mbar_expect_tx(bar + s * 8, kStBytes);
-            bulk_g2s(ring + s * kStBytes, a.packed + (size_t)(w0 + j) * kStBytes, kStBytes, bar + s * 8);
+        int j = 0;
+        for (int s = warp; s < R && j < nw; j++, s += kWarps)
+            fill_slot(ring + s * kStBytes, a.packed + (size_t)(w0 + j) * kStBytes, bar + s * 8, lane);
+        if (kL2PrefetchSt > 0 && a.l2_prefetch && j < nw && lane == 0) {
+            const uint32_t bytes = (uint32_t)min(nw - j, kL2PrefetchSt) * kStBytes;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
+                         ::"l"(a.packed + (size_t)(w0 + j) * kStBytes), "r"(bytes) : "memory");
         }
     }
     __syncwarp();
+    TL(1);
 
     // ---- everything below may depend on the previous kernel in the stream -------
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (a.late_release) asm volatile("griddepcontrol.launch_dependents;");
+    if (tracing) ts[1] = globaltimer();
+    TL(2);
+    // launch number of the fused all-reduce (written by this rank's previous such launch):
+    // requested here so that the load's latency hides behind the staging
+    unsigned ar_epoch_prev = 0;
+    if (kAr && a.ar_world > 0) ar_epoch_prev = __ldcg(a.ar_epoch + blockIdx.x);
 
     float fused_scale = 1.0f;
     if (FUSEDX) {
@@ -527,9 +605,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     } else if (I8) {
         stage_x_i8(reinterpret_cast<const int8_t*>(a.x), a.cols, xstage, sx, tid);
     } else {
-        stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid);
+        const int g0 = a.x_local ? (int)((unsigned)t0 % (unsigned)G) : 0;
+        stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
+                            a.x_local ? n : G);
     }
     __syncthreads();
+    TL(3);
 
     // ---- per-lane constants ------------------------------------------------------
     const int t = lane & 3, gq = lane >> 2;
@@ -545,6 +626,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     // ---- main loop: this warp's super-tiles, one ring slot each --------------------
     int rb = (int)((unsigned)w0 / (unsigned)G);
     int g = w0 - rb * G;
+    int gx_local = w0 - t0;                  // FP16 modes with x_local: where group g's activations were staged
     int seg = (rb - rb_first) + warp;        // partial-sum slot: unique per (warp, row block), ascending
     float acc[NB][4][2];                     // [block][field f][row half h]: rows 16f + gq + 8h of row block rb
 #pragma unroll
@@ -575,11 +657,24 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     };
 
     int slot = warp;
-    uint32_t par = 0;
+    uint32_t use = 0;                        // how often this slot has been filled before: sequence number / R
     for (int j = 0; j < nw; j++) {
-        ok = mbar_wait(bar + slot * 8, par);
+        // the slot's barrier must have reached the phase of this use before its parity means
+        // anything: the warp that emptied the slot publishes the use number when it refills it
+        if (use > 0) {
+            ok = false;
+#pragma unroll 1
+            for (int i = 0; i < (1 << 22); i++)
+                if (gen[slot] >= use) {
+                    ok = true;
+                    break;
+                }
+            if (!ok) break;
+        }
+        ok = mbar_wait(bar + slot * 8, use & 1u);
         if (!ok) break;
         const uint8_t* tile = ring_p + (size_t)slot * kStBytes;
+        const int gx = (!I8 && a.x_local) ? gx_local : g;
         const uint4* codes = reinterpret_cast<const uint4*>(tile) + lane;
         const uint4 s8 = *reinterpret_cast<const uint4*>(tile + kStCodeBytes + gq * 16);
 #pragma unroll
@@ -589,7 +684,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
 #pragma unroll
             for (int m = 0; m < 4; m++) {
                 const uint4 wd = codes[m * 32];
-                if ((m & 1) == 0) xb = xb_lane[((g * 2 + (m >> 1)) * NB + b) * kXbStride];
+                if ((m & 1) == 0) xb = xb_lane[((gx * 2 + (m >> 1)) * NB + b) * kXbStride];
                 const uint32_t b0 = (m & 1) ? xb.z : xb.x, b1 = (m & 1) ? xb.w : xb.y;
 #pragma unroll
                 for (int f = 0; f < 4; f++) {
@@ -604,10 +699,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
             int soff;
             if (I8) {
                 fx = 1.0f;
-                soff = sx[g];
+                soff = sx[gx];
             } else {
                 const int v = min(b * NV + (t >> 1), NVT - 1);
-                const uint2 c = reinterpret_cast<const uint2*>(xcst + g * NVT + v)[t & 1];
+                const uint2 c = reinterpret_cast<const uint2*>(xcst + gx * NVT + v)[t & 1];
                 fx = __uint_as_float(c.x);
                 soff = (int)c.y;
             }
@@ -625,20 +720,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         dirty = true;
         // refill this slot with sequence number u + R (it belongs to warp (u + R) mod 16)
         __syncwarp();
-        if (lane == 0) {
+        {
             const int u2 = j * kWarps + warp + R;
             const int w2 = u2 & (kWarps - 1), j2 = u2 >> kWarpsLog2;
             const int s2 = warp_start(w2, n);
             if (j2 < warp_start(w2 + 1, n) - s2) {
-                mbar_expect_tx(bar + slot * 8, kStBytes);
-                bulk_g2s(ring + slot * kStBytes, a.packed + (size_t)(t0 + s2 + j2) * kStBytes, kStBytes, bar + slot * 8);
+                if (lane == 0) gen[slot] = use + 1u;
+                fill_slot(ring + slot * kStBytes, a.packed + (size_t)(t0 + s2 + j2) * kStBytes, bar + slot * 8, lane);
             }
         }
         slot += kWarps;
         if (slot >= R) {
             slot -= R;
-            par ^= 1u;
+            use++;
         }
+        gx_local++;
         if (++g == G) {                      // row block finished (for this warp)
             flush();
             g = 0;
@@ -648,14 +744,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     }
     if (dirty) flush();
     if (!ok && lane == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+    TL(4);
     __syncthreads();
+    TL(5);
 
     // ---- reduction: warps of this CTA, then CTAs, row block by row block -----------
     const int nb = I8 ? 1 : a.batch;
     const float oscale = FUSEDX ? fused_scale : (I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f);
     constexpr int kRec = kStRows * NVT;      // floats of one row block's sums
 
-    if (a.ar_world > 0) {
+    if (kAr && a.ar_world > 0) {
         // ---- fused all-reduce: my partial sums go straight into every rank's receive
         // buffer over NVLink as 8-byte {value, launch number} words -- the store of a word
         // is atomic, so the launch number doubles as the arrival flag and no fence or
@@ -666,7 +764,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         // words that are still being read.
         __shared__ int ar_abort;
         if (tid == 0) ar_abort = 0;
-        const unsigned epoch = a.ar_epoch[blockIdx.x] + 1u;
+        if (tracing) ts[2] = globaltimer();
+        const unsigned epoch = ar_epoch_prev + 1u;
         const unsigned epar = epoch & 1u;
         const size_t wslot = (size_t)(epar * a.ar_world + a.ar_rank) * a.ar_rows_max;
         for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
@@ -679,54 +778,82 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
                 const int r = r_b * kStRows + idx;
                 if (r < a.rows) {
                     const uint2 word = make_uint2(__float_as_uint(s), epoch);
-                    for (int dst_rank = 0; dst_rank < a.ar_world; dst_rank++) {
-                        uint2* dst = a.ar_recv[dst_rank] + wslot + r;
-                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(word.x), "r"(word.y) : "memory");
+#pragma unroll
+                    for (int dst_rank = 0; dst_rank < kMaxPeers; dst_rank++) {
+                        if (dst_rank < a.ar_world) {
+                            uint2* dst = a.ar_recv[dst_rank] + wslot + r;
+                            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(word.x), "r"(word.y) : "memory");
+                        }
                     }
                 }
             }
         }
         __syncthreads();                     // ar_abort initialised; all stores issued
+        if (tracing) ts[3] = globaltimer();
         const int r_lo = rb_first * kStRows, r_hi = min(a.rows, (rb_last + 1) * kStRows);
         const uint2* recv = a.ar_recv[a.ar_rank] + (size_t)epar * a.ar_world * a.ar_rows_max;
+        const unsigned all = (1u << a.ar_world) - 1u;
         bool ok_ar = true;
         for (int r = r_lo + tid; r < r_hi; r += kThreads) {
-            float v = 0.f;
-            for (int src_rank = 0; src_rank < a.ar_world; src_rank++) {
-                const uint2* src = recv + (size_t)src_rank * a.ar_rows_max + r;
-                uint32_t val = 0, tag = 0;
-                // about half a second at most for the first wait that expires; once one has,
-                // every later wait of this CTA returns at its first look
+            // one look at ALL ranks' words per round (independent loads in flight together), then
+            // only at the missing ones.  About half a second at most for the first wait that
+            // expires; once one has, every later wait of this CTA gives up at its first look.
+            uint32_t val[kMaxPeers];
+            unsigned pending = all;
 #pragma unroll 1
-                for (int i = 0; i < (1 << 21); i++) {
-                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(tag) : "l"(src) : "memory");
-                    if (tag == epoch) break;
+            for (int i = 0; i < (1 << 21) && pending; i++) {
+                uint32_t tag[kMaxPeers];
+#pragma unroll
+                for (int d = 0; d < kMaxPeers; d++) {
+                    tag[d] = 0;
+                    if ((pending >> d) & 1u) {
+                        const uint2* src = recv + (size_t)d * a.ar_rows_max + r;
+                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val[d]), "=r"(tag[d]) : "l"(src) : "memory");
+                    }
+                }
+#pragma unroll
+                for (int d = 0; d < kMaxPeers; d++)
+                    if (((pending >> d) & 1u) && tag[d] == epoch) pending &= ~(1u << d);
+                if (pending) {
                     if (*(volatile int*)&ar_abort) break;
-                    __nanosleep(32);
+                    __nanosleep(20);
                 }
-                if (tag != epoch) {
-                    ok_ar = false;
-                    ar_abort = 1;
-                }
-                v += __uint_as_float(val);
             }
+            if (pending) {
+                ok_ar = false;
+                ar_abort = 1;
+            }
+            float v = 0.f;
+#pragma unroll
+            for (int d = 0; d < kMaxPeers; d++)
+                if (d < a.ar_world) v += __uint_as_float(val[d]);      // rank order: the same sum on every rank
             a.y[r] = __float2half_rn(v);
         }
         if (!ok_ar) atomicExch(a.err, TLLM_ERR_TIMEOUT);
         __syncthreads();
         if (tid == 0) a.ar_epoch[blockIdx.x] = epoch;
+        if (tracing) {
+            ts[4] = globaltimer();
+            unsigned long long* rec = a.ar_trace + (size_t)(epoch % (unsigned)a.ar_trace_cap) * 8;
+#pragma unroll
+            for (int i = 0; i < 5; i++) rec[i] = ts[i];
+            rec[5] = epoch;
+        }
         return;
     }
 
-    float* myrec = a.ws + (size_t)blockIdx.x * a.ws_stride;
+    uint2* myrec = a.ws + (size_t)blockIdx.x * a.ws_stride;
     const int rec1 = a.ws_stride >> 1;        // offset of a CTA's second record
+    constexpr int kW = kRec / 32;             // words per lane in one record
+    constexpr int kChunk = (kW >= 8) ? 1 : ((kW >= 4) ? 2 : 4);      // records polled together
+    bool ok_c = true;
     for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
         const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);     // this CTA's super-tiles of the block
         const int wa = warp_of(ta - t0, n), wb = warp_of(tb - 1 - t0, n);
         const bool full = (tb - ta == G);
-        float s[kRec / 32];
+        float s[kW];
 #pragma unroll
-        for (int i = 0; i < kRec / 32; i++) {
+        for (int i = 0; i < kW; i++) {
             const int idx = lane + 32 * i;
             float v = 0.f;
             for (int w = wa; w <= wb; w++)
@@ -734,53 +861,85 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
                     v += part[(size_t)((r_b - rb_first) + w) * kRec + idx];
             s[i] = v;
         }
-        if (full) {
+        if (!full) {
+            // This row block is shared with neighbouring CTAs (K is split across them).  All but
+            // the last of them publish their sums and are done; the last gathers.
+            const int c_a = part_of(r_b * G, a.part_q, a.part_r);
+            const int c_b = part_of((r_b + 1) * G - 1, a.part_q, a.part_r);
+            if ((int)blockIdx.x != c_b) {
+                uint2* rec = myrec + ((r_b == rb_first) ? 0 : rec1);
 #pragma unroll
-            for (int i = 0; i < kRec / 32; i++) {
-                const int idx = lane + 32 * i;
-                const int r = r_b * kStRows + idx / NVT, b = idx % NVT;
-                if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(s[i] * oscale);
+                for (int i = 0; i < kW; i++)
+                    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};"
+                                 ::"l"(rec + lane + 32 * i), "r"(__float_as_uint(s[i])), "r"(1u) : "memory");
+                continue;
             }
-        } else {
-            // this row block is shared with neighbouring CTAs: publish the partial sums;
-            // the contributor that arrives last adds all records in CTA order
-            const int k = (r_b == rb_first) ? 0 : 1;
+            float tot[kW];
 #pragma unroll
-            for (int i = 0; i < kRec / 32; i++) myrec[k * rec1 + lane + 32 * i] = s[i];
-            __threadfence();
-            __syncwarp();
-            int c_a = 0, c_b = 0, last = 0;
-            if (lane == 0) {
-                c_a = part_of(r_b * G, a.part_q, a.part_r);
-                c_b = part_of((r_b + 1) * G - 1, a.part_q, a.part_r);
-                const int prev = atomicAdd(a.counters + r_b, 1);
-                last = (prev == c_b - c_a) ? 1 : 0;
-            }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-                c_a = __shfl_sync(0xffffffffu, c_a, 0);
-                c_b = __shfl_sync(0xffffffffu, c_b, 0);
-                float tot[kRec / 32];
+            for (int i = 0; i < kW; i++) tot[i] = 0.f;
+            for (int c0 = c_a; c0 < c_b; c0 += kChunk) {
+                uint2* rec[kChunk];
+                uint32_t val[kChunk][kW];
+                unsigned pending = 0;
 #pragma unroll
-                for (int i = 0; i < kRec / 32; i++) tot[i] = 0.f;
-                for (int c = c_a; c <= c_b; c++) {
+                for (int cc = 0; cc < kChunk; cc++) {
+                    const int c = min(c0 + cc, c_b - 1);
                     // record 0 of a CTA belongs to its first row block, record 1 to its last
                     const int c_rb = (int)((unsigned)part_start(c, a.part_q, a.part_r) / (unsigned)G);
-                    const float* rec = a.ws + (size_t)c * a.ws_stride + ((r_b == c_rb) ? 0 : rec1);
-#pragma unroll
-                    for (int i = 0; i < kRec / 32; i++) tot[i] += __ldcg(rec + lane + 32 * i);
+                    rec[cc] = a.ws + (size_t)c * a.ws_stride + ((r_b == c_rb) ? 0 : rec1) + lane;
+                    if (c0 + cc < c_b) pending |= ((1u << kW) - 1u) << (cc * kW);
                 }
+                // all words of the chunk are requested together, then only the missing ones; a
+                // wait that expires (about half a second) ends every later wait of this CTA at once
+#pragma unroll 1
+                for (int it = 0; it < (1 << 21) && pending; it++) {
+                    uint32_t v[kChunk][kW], f[kChunk][kW];
 #pragma unroll
-                for (int i = 0; i < kRec / 32; i++) {
-                    const int idx = lane + 32 * i;
-                    const int r = r_b * kStRows + idx / NVT, b = idx % NVT;
-                    if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(tot[i] * oscale);
+                    for (int cc = 0; cc < kChunk; cc++)
+#pragma unroll
+                        for (int i = 0; i < kW; i++) {
+                            f[cc][i] = 0;
+                            if ((pending >> (cc * kW + i)) & 1u)
+                                asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];"
+                                             : "=r"(v[cc][i]), "=r"(f[cc][i]) : "l"(rec[cc] + 32 * i) : "memory");
+                        }
+#pragma unroll
+                    for (int cc = 0; cc < kChunk; cc++)
+#pragma unroll
+                        for (int i = 0; i < kW; i++)
+                            if (f[cc][i]) {
+                                val[cc][i] = v[cc][i];
+                                pending &= ~(1u << (cc * kW + i));
+                            }
+                    if (pending) {
+                        if (!ok_c) break;
+                        __nanosleep(20);
+                    }
                 }
-                if (lane == 0) a.counters[r_b] = 0;
+                if (pending) ok_c = false;
+#pragma unroll
+                for (int cc = 0; cc < kChunk; cc++)
+                    if (c0 + cc < c_b) {
+#pragma unroll
+                        for (int i = 0; i < kW; i++) {
+                            tot[i] += __uint_as_float(val[cc][i]);
+                            asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %1};"
+                                         ::"l"(rec[cc] + 32 * i), "r"(0u) : "memory");
+                        }
+                    }
             }
+#pragma unroll
+            for (int i = 0; i < kW; i++) s[i] += tot[i];            // own part last: CTA order
+        }
+#pragma unroll
+        for (int i = 0; i < kW; i++) {
+            const int idx = lane + 32 * i;
+            const int r = r_b * kStRows + idx / NVT, b = idx % NVT;
+            if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(s[i] * oscale);
         }
     }
+    if (!ok_c) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+    TL(6);
 }
 
 // ---------------------------------------------------------------------------
@@ -861,8 +1020,7 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ packed, uint32_t* __re
 // ---------------------------------------------------------------------------
 constexpr int kMaxRowBlocks = 1 << 16;          // rows up to 4,194,304
 struct DeviceScratch {
-    float* ws = nullptr;       // [kTickets][kMaxCtas][2][kRecFloats]
-    int* counters = nullptr;   // [kTickets][kMaxRowBlocks]
+    uint2* ws = nullptr;       // [kTickets][kMaxCtas][2][kRecFloats] {value, flag}, all zero between launches
     int* misc = nullptr;       // [0] non-canonical bit counter of the last prepare, [1] device error flag
     int sms = 0;
     unsigned ticket = 0;
@@ -881,11 +1039,10 @@ static int get_scratch(DeviceScratch** out)
         // First use on this device: allocate and zero the scratch.  Must not happen
         // inside a stream capture; make one call per device before capturing.
         cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaMalloc(&s.ws, (size_t)kTickets * kMaxCtas * 2 * kRecFloats * sizeof(float)) != cudaSuccess ||
-            cudaMalloc(&s.counters, (size_t)kTickets * kMaxRowBlocks * sizeof(int)) != cudaSuccess ||
+        if (cudaMalloc(&s.ws, (size_t)kTickets * kMaxCtas * 2 * kRecFloats * sizeof(uint2)) != cudaSuccess ||
             cudaMalloc(&s.misc, 64) != cudaSuccess)
             return fail(TLLM_ERR_LAUNCH, "scratch allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
-        cudaMemset(s.counters, 0, (size_t)kTickets * kMaxRowBlocks * sizeof(int));
+        cudaMemset(s.ws, 0, (size_t)kTickets * kMaxCtas * 2 * kRecFloats * sizeof(uint2));
         cudaMemset(s.misc, 0, 64);
         cudaDeviceSynchronize();
         s.ready = true;
@@ -928,47 +1085,60 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     if ((long long)nrb * a.groups >= (1ll << 26))
         return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: more than 2^26 super-tiles", rows, cols);
     const int tiles = nrb * a.groups;
-    int grid = sms < max_ctas ? sms : max_ctas;
-    // Whole row blocks per CTA when that keeps the SMs at least 80 % evenly loaded: no
-    // row block then spans two CTAs and the cross-CTA combine never runs.  Otherwise
-    // split at super-tile granularity (K is split across CTAs).
-    const int per_cta_rb = (nrb + grid - 1) / grid;
-    a.aligned = (nrb >= grid && (double)nrb / ((double)per_cta_rb * grid) >= 0.8) ? 1 : 0;
-    // Fewer row blocks than SMs and short rows (one super-tile per warp at most): such a
-    // matrix is a few hundred KB, latency-bound, and the cross-CTA combine would cost more
-    // than the idle SMs; one CTA per row block.
-    if (nrb < grid && a.groups <= kWarps) a.aligned = 1;
-    // The same holds with a few more row blocks than SMs when a CTA's share is still at most
-    // one super-tile per warp.
-    if (per_cta_rb * a.groups <= kWarps) a.aligned = 1;
-    if (force_aligned) a.aligned = 1;
-    const int items = a.aligned ? nrb : tiles;
-    if (items < grid) grid = items;
-    a.part_q = items / grid;
-    a.part_r = items % grid;
-    a.late_release = release_rule(rows, cols);
-    // shared memory: activations | group constants | partial sums | (fused staging) | mbarriers | ring
+    const int grid_max = sms < max_ctas ? sms : max_ctas;
     const bool fusedx = (mode == kI8Norm || mode == kI8Silu || mode == kI8Quant);
     const bool i8 = (mode == kI8 || fusedx);
-    size_t off = i8 ? (size_t)cols : (size_t)a.groups * nvt * 384;
-    off = (off + 15) & ~(size_t)15;
-    a.off_xcst = (int)off;
-    off += i8 ? (size_t)a.groups * sizeof(int) : (size_t)a.groups * nvt * 16;
-    off = (off + 15) & ~(size_t)15;
-    a.off_part = (int)off;
-    const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * (a.aligned ? a.groups : 1);     // super-tiles of the largest CTA
-    const int max_rb_per_cta = a.aligned ? (a.part_q + 1) : ((a.part_q + 1 + a.groups - 1) / a.groups + 1);
-    off += (size_t)(max_rb_per_cta + kWarps) * kStRows * nvt * sizeof(float);
-    if (fusedx) {
+    const int per_cta_rb = (nrb + grid_max - 1) / grid_max;
+
+    // Shared-memory layout for one way of cutting the matrix: activations | group constants |
+    // partial sums | (fused staging) | mbarriers | use numbers | ring.  Returns the bytes in
+    // front of the ring.
+    auto layout = [&](int aligned, int* grid, int* n_max_out) {
+        a.aligned = aligned;
+        const int items = aligned ? nrb : tiles;
+        *grid = items < grid_max ? items : grid_max;
+        a.part_q = items / *grid;
+        a.part_r = items % *grid;
+        const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * (aligned ? a.groups : 1);    // super-tiles of the largest CTA
+        *n_max_out = n_max;
+        a.x_local = (!i8 && n_max < a.groups) ? 1 : 0;
+        const int gstaged = a.x_local ? n_max : a.groups;
+        size_t off = i8 ? (size_t)cols : (size_t)gstaged * nvt * 384;
         off = (off + 15) & ~(size_t)15;
-        a.off_xtmp = (int)off;
-        off += (size_t)cols * sizeof(half) + 64 * sizeof(float);
-    }
-    off = (off + 15) & ~(size_t)15;
-    a.off_bar = (int)off;
-    off += (size_t)kMaxSlots * 8;
-    off = (off + 127) & ~(size_t)127;
-    a.off_ring = (int)off;
+        a.off_xcst = (int)off;
+        off += i8 ? (size_t)a.groups * sizeof(int) : (size_t)gstaged * nvt * 16;
+        off = (off + 15) & ~(size_t)15;
+        a.off_part = (int)off;
+        const int max_rb_per_cta = aligned ? (a.part_q + 1) : ((a.part_q + 1 + a.groups - 1) / a.groups + 1);
+        off += (size_t)(max_rb_per_cta + kWarps) * kStRows * nvt * sizeof(float);
+        if (fusedx) {
+            off = (off + 15) & ~(size_t)15;
+            a.off_xtmp = (int)off;
+            off += (size_t)cols * sizeof(half) + 64 * sizeof(float);
+        }
+        off = (off + 15) & ~(size_t)15;
+        a.off_bar = (int)off;
+        off += (size_t)kMaxSlots * 8;
+        a.off_gen = (int)off;
+        off += (size_t)kMaxSlots * 4;
+        off = (off + 127) & ~(size_t)127;
+        a.off_ring = (int)off;
+        return off;
+    };
+
+    // Whole row blocks per CTA -- no row block then spans two CTAs and nothing is combined across
+    // CTAs -- in two cases: when that keeps the SMs at least 80 % evenly loaded; and when a CTA's
+    // whole share of row blocks fits the ring that two co-resident CTAs allow, however few CTAs
+    // that leaves: such a launch has all its weights on the chip before the kernel in front of
+    // it ends, so its time after that is a few hundred nanoseconds of arithmetic either way,
+    // while a combine across CTAs costs a store, a load and a poll on top.  Otherwise the
+    // matrix is cut at super-tile granularity (K is split across CTAs).
+    int grid = 0, n_max = 0;
+    size_t off = layout(1, &grid, &n_max);
+    bool aligned = force_aligned || (nrb >= grid_max && (double)nrb / ((double)per_cta_rb * grid_max) >= 0.8);
+    if (!aligned && off + (size_t)n_max * kStBytes <= kCoResidentBytes && n_max <= kMaxSlots) aligned = true;
+    if (!aligned) off = layout(0, &grid, &n_max);
+    a.late_release = release_rule(rows, cols);
     // Ring: what a CTA can use, bounded by what lets two CTAs share the SM (the launch that
     // follows prefetches its weights beside this one); a problem whose activations leave less
     // than 24 slots that way runs one CTA per SM with all of the shared memory.
@@ -977,16 +1147,17 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     if (slots < want && slots < 24) slots = ((long long)kMaxSmemBytes - (long long)off) / kStBytes;
     if (slots > want) slots = want;
     if (slots < kWarps)
-        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d needs more shared memory than an SM has (%zu bytes before the ring)",
-                    rows, cols, off);
+        return fail(TLLM_ERR_SIZE, "rows=%d cols=%d with %d vectors per pass needs more shared memory than an SM has "
+                    "(%zu bytes before the ring)", rows, cols, nvt, off);
     a.ring_slots = (int)slots;
+    a.l2_prefetch = (n_max > (int)slots) ? 1 : 0;
     off += (size_t)slots * kStBytes;
     *grid_out = grid;
     *smem_out = off;
     return TLLM_OK;
 }
 
-template <int MODE, int NB, int NV>
+template <int MODE, int NB, int NV, bool AR = false>
 static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     static bool attr[64] = {};
@@ -996,9 +1167,16 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     {
         std::lock_guard<std::mutex> lk(mu);
         if (dev >= 0 && dev < 64 && !attr[dev]) {
-            cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmemBytes);
-            cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared);
+            const cudaError_t e1 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR>,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmemBytes);
+            const cudaError_t e2 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR>,
+                                                        cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                        cudaSharedmemCarveoutMaxShared);
+            if (e1 != cudaSuccess || e2 != cudaSuccess) {
+                cudaGetLastError();
+                return fail(TLLM_ERR_LAUNCH, "gemv_packed shared-memory set-up: %s",
+                            cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+            }
             attr[dev] = true;
         }
     }
@@ -1012,7 +1190,7 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_packed_kernel<MODE, NB, NV>, a);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_packed_kernel<MODE, NB, NV, AR>, a);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(TLLM_ERR_LAUNCH, "gemv_packed launch: %s", cudaGetErrorString(e));
@@ -1095,7 +1273,6 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     }
     a.ws = s->ws + (size_t)ticket * kMaxCtas * 2 * kRecFloats;
     a.ws_stride = 2 * kRecFloats;
-    a.counters = s->counters + (size_t)ticket * kMaxRowBlocks;
     a.err = s->misc + 1;
     return dispatch(a, mode, grid, smem, stream);
 }
@@ -1173,12 +1350,20 @@ int launch_gemv_int8_packed_quant(const uint8_t* packed, const half* x, half* y,
 int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch, int rows, int cols,
                        cudaStream_t stream)
 {
-    // up to four vectors share one pass over the weights; larger batches take ceil(B/4) passes
-    for (int b0 = 0; b0 < batch; b0 += kMaxVec) {
-        const int nb = (batch - b0 >= kMaxVec) ? kMaxVec : (batch - b0);
+    // up to four vectors share one pass over the weights; larger batches take ceil(B/4) passes.
+    // Where the staged activations of that many vectors do not fit beside a ring in shared
+    // memory (very long rows), fewer vectors share a pass.
+    int per = kMaxVec;
+    for (int b0 = 0; b0 < batch;) {
+        const int nb = (batch - b0 >= per) ? per : (batch - b0);
         const int st = launch_packed_once(packed, x + (size_t)b0 * cols, y + (size_t)b0 * rows, 1.0f, kF16, nb, rows, cols,
                                           stream);
+        if (st == TLLM_ERR_SIZE && per > 1) {
+            per >>= 1;
+            continue;
+        }
         if (st) return st;
+        b0 += nb;
     }
     return TLLM_OK;
 }
@@ -1191,16 +1376,13 @@ int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch,
 // the allocator is forbidden (a real-time loop, a stream capture), or a process whose
 // memory budget is audited up front.  For them the split-K combine scratch of the
 // GEMV lives in this fixed array instead of a lazily allocated buffer.  Every GPU that
-// loads the library carries these 84 KB until the process exits.
-//   [0, 81920)        partial-sum records, kNoAllocMaxCtas x 2 x 64 floats (one vector)
-//   [81920, 86016)    arrival counters, kNoAllocMaxRowBlocks ints
-//   [86016, 86020)    device error flag
+// loads the library carries these 160 KB until the process exits.
+//   [0, 163840)       partial-sum records, kNoAllocMaxCtas x 2 x 64 words {value, flag} (one vector)
+//   [163840, 163844)  device error flag
 constexpr int kNoAllocMaxRows = 65536;
-constexpr int kNoAllocMaxRowBlocks = kNoAllocMaxRows / kStRows;
 constexpr int kNoAllocMaxCtas = 160;
-constexpr size_t kNoAllocWsBytes = (size_t)kNoAllocMaxCtas * 2 * kStRows * sizeof(float);
-constexpr size_t kNoAllocCounterBytes = (size_t)kNoAllocMaxRowBlocks * sizeof(int);
-constexpr size_t kNoAllocBytes = kNoAllocWsBytes + kNoAllocCounterBytes + 256;
+constexpr size_t kNoAllocWsBytes = (size_t)kNoAllocMaxCtas * 2 * kStRows * sizeof(uint2);
+constexpr size_t kNoAllocBytes = kNoAllocWsBytes + 256;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 struct NoAllocDevice {
@@ -1238,10 +1420,10 @@ static int noalloc_device(NoAllocDevice** out)
 // device looks up the device address of the scratch array (cudaGetSymbolAddress, with
 // that device current) and raises the kernel's shared-memory limit; make that first
 // call outside any stream capture.  All calls share the one scratch array, which
-// keeps what the previous call left: the counters are cleared on `stream` before each
-// launch, and two calls whose kernels overlap on the GPU (different streams) race.
-// With one vector a partial record is 64 floats, so the records are laid out at that
-// stride here (ws_stride), and the grid is capped at kNoAllocMaxCtas.
+// keeps what the previous call left: the records (their flags must start at zero) are
+// cleared on `stream` before each launch, and two calls whose kernels overlap on the GPU
+// (different streams) race.  With one vector a partial record is 64 words, so the records
+// are laid out at that stride here (ws_stride), and the grid is capped at kNoAllocMaxCtas.
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream)
 {
@@ -1261,15 +1443,13 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     int grid = 0;
     size_t smem = 0;
     if ((st = plan_gemv(a, nd->sms, kF16, 1, kNoAllocMaxCtas, false, &grid, &smem))) return st;
-    a.ws = reinterpret_cast<float*>(nd->base);
-    a.counters = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
-    a.err = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes + kNoAllocCounterBytes);
+    a.ws = reinterpret_cast<uint2*>(nd->base);
+    a.err = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
     a.ws_stride = 2 * kStRows;
-    // the counters must start at zero; a call that was cut short may have left some set
-    const int nrb = (rows + kStRows - 1) / kStRows;
-    if (cudaMemsetAsync(a.counters, 0, (size_t)nrb * sizeof(int), stream) != cudaSuccess) {
+    // the records' flags must start at zero; a call that was cut short may have left some set
+    if (cudaMemsetAsync(a.ws, 0, (size_t)grid * 2 * kStRows * sizeof(uint2), stream) != cudaSuccess) {
         cudaGetLastError();
-        return fail(TLLM_ERR_LAUNCH, "clearing the scratch counters failed");
+        return fail(TLLM_ERR_LAUNCH, "clearing the scratch records failed");
     }
     return dispatch(a, kF16, grid, smem, stream);
 }
@@ -1281,7 +1461,7 @@ int noalloc_error_check(cudaStream_t stream)
     NoAllocDevice* nd = nullptr;
     int st = noalloc_device(&nd);
     if (st) return st;
-    int* flag_dev = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes + kNoAllocCounterBytes);
+    int* flag_dev = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
     int flag = 0;
     if (cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
         cudaStreamSynchronize(stream) != cudaSuccess)
@@ -1290,6 +1470,22 @@ int noalloc_error_check(cudaStream_t stream)
         cudaMemsetAsync(flag_dev, 0, sizeof(int), stream);
         return fail(flag, "a kernel reported status %d (bounded wait expired)", flag);
     }
+    return TLLM_OK;
+}
+
+// Time-stamp buffer of the fused all-reduce per device (see GemvArgs::ar_trace); set by
+// allreduce_set_trace, nullptr = off.
+struct ArTrace { unsigned long long* buf = nullptr; int cap = 0; };
+static ArTrace g_ar_trace[64];
+
+int allreduce_set_trace(void* buffer, int records)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(TLLM_ERR_DEVICE, "no usable current device");
+    if (buffer && records < 1) return fail(TLLM_ERR_SIZE, "trace buffer of %d records", records);
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ar_trace[dev].buf = static_cast<unsigned long long*>(buffer);
+    g_ar_trace[dev].cap = buffer ? records : 0;
     return TLLM_OK;
 }
 
@@ -1316,7 +1512,6 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
     size_t smem = 0;
     if ((st = plan_gemv(a, s->sms, kF16, 1, kMaxCtas, true, &grid, &smem))) return st;
     a.ws = s->ws;                       // unused in the aligned split
-    a.counters = s->counters;
     a.err = s->misc + 1;
     a.ws_stride = 2 * kRecFloats;
     a.ar_world = world;
@@ -1324,7 +1519,16 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
     a.ar_rows_max = rows_max;
     for (int d = 0; d < world; d++) a.ar_recv[d] = static_cast<uint2*>(peer_recv[d]);
     a.ar_epoch = static_cast<unsigned*>(epoch_local);
-    return dispatch(a, kF16, grid, smem, stream);
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (dev >= 0 && dev < 64) {
+            a.ar_trace = g_ar_trace[dev].buf;
+            a.ar_trace_cap = g_ar_trace[dev].cap;
+        }
+    }
+    return launch_mode<kF16, 1, 1, true>(a, grid, smem, stream);
 }
 
 int launch_gemv_int8_packed(const uint8_t* packed, const int8_t* xq, float in_scale, half* y, int rows,
@@ -1402,3 +1606,14 @@ int weight_unregister(const void* nz)
 }
 
 }  // namespace tllm
+
+#ifdef TLLM_TIMELINE
+// host_out: [8][256][8] time stamps, counts: [256] launches seen per CTA index.
+extern "C" int tllm_b200_timeline_read(unsigned long long* host_out, unsigned* counts)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(host_out, tllm::g_tl, sizeof(tllm::g_tl)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(counts, tllm::g_tl_cnt, sizeof(tllm::g_tl_cnt)) != cudaSuccess) return -1;
+    return 0;
+}
+#endif

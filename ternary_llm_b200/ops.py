@@ -246,6 +246,20 @@ class FusedAllReduce:
         ptrs = list(self.handle.buffer_ptrs)
         self.recv = (ctypes.c_void_p * self.world)(*ptrs)
         self.epoch = torch.zeros(AR_MAX_CTAS, dtype=torch.int32, device=device)
+        self._trace = None
+
+    def trace(self, records: int = 0):
+        """records > 0: start recording the time stamps of this device's fused all-reduce
+        launches (tllm_b200_allreduce_trace) into a buffer of that many records; 0: stop and
+        return what was recorded as an int64 array [n, 8] (see the header for the fields)."""
+        if records > 0:
+            self._trace = torch.zeros(records, 8, dtype=torch.int64, device=self.epoch.device)
+            _lib.check(_lib.lib().tllm_b200_allreduce_trace(self._trace.data_ptr(), records))
+            return None
+        _lib.check(_lib.lib().tllm_b200_allreduce_trace(None, 0))
+        out, self._trace = self._trace, None
+        torch.cuda.synchronize()
+        return None if out is None else out.cpu().numpy()
 
 
 def ternary_gemv_packed_allreduce(w: PreparedWeight, input, output, ar: FusedAllReduce) -> None:

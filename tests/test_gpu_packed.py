@@ -181,7 +181,9 @@ def test_gemv_packed_linearity_at_full_size():
     x = np.random.default_rng(8).standard_normal((1, k)).astype(np.float16)
     y1 = _run_packed(w, x)
     y2 = _run_packed(w, (2 * x.astype(np.float32)).astype(np.float16))
-    assert np.array_equal(2 * y1.astype(np.float32), y2.astype(np.float32))
+    normal = np.abs(y1.astype(np.float32)) >= 2.0 ** -13     # FP16 subnormals round on a fixed grid
+    assert np.array_equal(2 * y1.astype(np.float32)[normal], y2.astype(np.float32)[normal])
+    assert (np.abs(2 * y1.astype(np.float32) - y2.astype(np.float32)) <= 2.0 ** -23).all()
     # negation is exact up to the FP32 rounding of the two digit halves: at most one
     # FP16 ulp on a few elements
     yn = _run_packed(w, -x)

@@ -72,7 +72,14 @@ def test_gemv_batched_at_8b_shapes(name, batch):
     torch.cuda.synchronize()
     tl.check_device_errors()
     _check_rows(y.cpu().numpy(), nz, sg, sc, _sample_rows(n, seed=batch), x, f"gemv {name} batch {batch}")
-    assert torch.equal(y2.float(), y.float() * 2), "W(2x) != 2 W(x)"
+    if batch <= 8:      # the integer-MMA GEMV: scaling by two only shifts the block exponent
+        # (exact wherever the FP16 result is a normal number; a subnormal one rounds on a fixed grid)
+        normal = y.float().abs() >= 2.0 ** -13
+        assert torch.equal(y2.float()[normal], y.float()[normal] * 2), "W(2x) != 2 W(x)"
+        assert bool(((y2.float() - 2 * y.float()).abs() <= 2.0 ** -23).all())
+    else:               # the tcgen05 route: FP16 x FP16 products summed in hardware, to one last place
+        d = (y2.float() - 2 * y.float()).abs()
+        assert bool((d <= (2 * y.float()).abs() * 2.0 ** -10 + 1e-6).all()), "W(2x) differs from 2 W(x) by more than one ulp"
 
 
 GEMM_CASES = [(m, s) for s in ("gate/up", "down") for m in (128, 512, 2048)] + [(2048, "k/v"), (2048, "q/o")]
