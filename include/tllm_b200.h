@@ -110,9 +110,9 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B,
 /* ------------------------------------------------------------------------
  * Prepared weights (load-time repack).
  *
- * The streaming tensor-core GEMV reads a kernel-friendly layout: super-tiles of 64 rows
- * x 128 columns, 2 bits per weight (offset codes t + 1 arranged so that one AND makes an
- * MMA operand register), FP16 scales beside them (ternary_llm_b200/csrc/packed_layout.cuh).  It is derived once per
+ * The streaming tensor-core GEMV reads a kernel-friendly layout: tiles of 16 rows x 128
+ * columns, 2 bits per weight (offset codes t + 1 arranged so that one AND makes an MMA
+ * operand register), FP16 scales beside them (ternary_llm_b200/csrc/packed_layout.cuh).  It is derived once per
  * matrix at load time from the three reference arrays -- the hook sits right
  * after the reference loader's read_ternary_weight (src/model.cpp:46-60) -- and is
  * lossless for canonical masks (no sign bit without its nonzero bit), which is
@@ -122,7 +122,7 @@ int tllm_b200_gemm(const void* A, const uint32_t* nz_B, const uint32_t* sign_B,
  * ------------------------------------------------------------------------ */
 
 /* Size in bytes of the packed form of a [rows, cols] matrix (cols % 128 == 0); rows are
- * padded to a multiple of 64 in it. */
+ * padded to a multiple of 16 in it. */
 size_t tllm_b200_packed_bytes(int rows, int cols);
 
 /*
@@ -170,7 +170,7 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
  * of tllm_b200_gemv_packed up to the order of the FP32 additions over K.  packed, y, rows
  * are HOST arrays of length count.
  * Fastest when the matrices were packed back to back -- packed[i+1] == packed[i] +
- * tllm_b200_packed_bytes(rows[i], cols) with every rows[i] but the last a multiple of 64
+ * tllm_b200_packed_bytes(rows[i], cols) with every rows[i] but the last a multiple of 16
  * (prepare them into consecutive pieces of one buffer): they are then streamed as ONE
  * matrix in one launch.  Otherwise one launch per matrix.
  */
@@ -190,8 +190,8 @@ int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* cons
  *   peer_recv[d] : rank d's receive buffer, 8-byte words [2][world][rows_max], as mapped in
  *                  THIS process (peer / symmetric memory), zeroed before first use
  *   epoch_local  : this rank's launch counters, uint32 [TLLM_AR_MAX_CTAS], zeroed
- * All ranks must issue the same sequence of these calls.  Each CTA owns whole 64-row
- * blocks (one block per CTA while rows <= 64 x number of SMs).  A wait that expires sets
+ * All ranks must issue the same sequence of these calls.  Each CTA owns whole 16-row
+ * blocks.  A wait that expires sets
  * the device error flag (tllm_b200_check_device_errors); after the first one that expires
  * in a CTA, its remaining waits of that launch return at once.
  */
@@ -216,7 +216,7 @@ int tllm_b200_allreduce_trace(void* buffer, int records);
  * allocate device memory (a server that owns all of HBM through its own arena, a
  * real-time loop, a host that audits allocations up front).  It has no counterpart
  * in the reference.  Nothing is allocated, by this call or any routine it uses: the
- * split-K scratch is a fixed 160 KB array inside the library image, present on every
+ * split-K scratch is a fixed 40 KB array inside the library image, present on every
  * GPU that loads the library until the process exits.
  * Limits: rows <= 65536 (TLLM_ERR_SIZE beyond), cols as for tllm_b200_gemv_packed.
  * The first call on a device resolves the array's device address and configures the

@@ -57,10 +57,10 @@ struct Cfg {
 };
 
 struct Args {
-    const uint8_t* packed;     // packed weights [ceil(N/64)][K/128] super-tiles
+    const uint8_t* packed;     // packed weights [ceil(N/16)][K/128] tiles
     half* C;                   // [M, N]
     int M, N, K, groups;       // groups = K / 128
-    int nrb;                   // ceil(N / 64)
+    int nrb;                   // ceil(N / 16)
     int* err;
     // split-K (gridDim.z > 1): CTA z contracts stages [z*groups/ks, (z+1)*groups/ks) and writes an
     // FP32 partial tile; the CTA of a tile that arrives last adds the partials in z order.
@@ -259,26 +259,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
         // ---------------- weight expanders, then epilogue ----------------
         const int row = tid - 128;                       // feature row inside the tile = TMEM lane
         const int n = n0 + row;
-        const int rb = n >> 6, r64 = n & 63;             // super-tile row block and row inside it
-        const int f = r64 >> 4, gq = r64 & 7, h = (r64 >> 3) & 1;
+        const int rb = n >> 4, r16 = n & 15;             // 16-row block and row inside it
+        const int gq = r16 & 7, h = r16 >> 3;
         const bool row_valid = rb < a.nrb;               // rows past the matrix expand to zeros
-        const uint8_t* tile0 = a.packed + ((size_t)(row_valid ? rb : 0) * a.groups + it0) * kStBytes;
-        // this row's code words of step m, lane t: the pair (column halves j2 = 0, 1) at
-        // word index (m*32 + gq*4 + t)*4 + 2h, i.e. one 64-bit load per (m, t)
-        const int pair0 = (gq * 4) * 2 + h;              // in units of uint2; + m*64 + t*2
-        const int spos = st_scale_index(r64);
-        const int sh = 2 * f;
+        const uint8_t* tile0 = a.packed + ((size_t)(row_valid ? rb : 0) * a.groups + it0) * kTileBytes;
+        // this row's code words of MMA lane t: the pair (column halves j2 = 0, 1) at word index
+        // (gq*4 + t)*4 + 2h, i.e. one 64-bit load per t; each word holds all four 32-column steps
+        const int pair0 = (gq * 4) * 2 + h;              // in units of uint2; + t*2
+        const int spos = tile_scale_index(r16);
         const uint32_t lane_base = tmem + ((uint32_t)(row & ~31) << 16);   // this warp's 32 TMEM lanes
 
-        uint2 cw[4][4];
+        uint2 cw[4];
         uint32_t sbits = 0;
         auto load_stage = [&](const uint8_t* tp) {
             const uint2* p = reinterpret_cast<const uint2*>(tp) + pair0;
 #pragma unroll
-            for (int m = 0; m < 4; m++)
-#pragma unroll
-                for (int t = 0; t < 4; t++) cw[m][t] = __ldg(p + m * 64 + t * 2);
-            sbits = __half_as_ushort(__ldg(reinterpret_cast<const half*>(tp + kStCodeBytes) + spos));
+            for (int t = 0; t < 4; t++) cw[t] = __ldg(p + t * 2);
+            sbits = __half_as_ushort(__ldg(reinterpret_cast<const half*>(tp + kTileCodeBytes) + spos));
         };
         if (row_valid) load_stage(tile0);
         bool ok = true;
@@ -286,24 +283,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const Args a)
             const int sa = it % kAStages;
             // PRMT table of this stage: bytes 0,1 = -s (code 0), 2,3 = 0 (code 1), 4,5 = +s (code 2)
             const uint32_t tab_lo = row_valid ? (sbits ^ 0x8000u) : 0u, tab_hi = row_valid ? sbits : 0u;
-            uint2 cur[4][4];
+            uint2 cur[4];
 #pragma unroll
-            for (int m = 0; m < 4; m++)
-#pragma unroll
-                for (int t = 0; t < 4; t++) cur[m][t] = cw[m][t];
-            if (it + 1 < nstages && row_valid) load_stage(tile0 + (size_t)(it + 1) * kStBytes);   // prefetch the next group
+            for (int t = 0; t < 4; t++) cur[t] = cw[t];
+            if (it + 1 < nstages && row_valid) load_stage(tile0 + (size_t)(it + 1) * kTileBytes);   // prefetch the next group
             if (!mbar_wait(empty_a(sa), ((it / kAStages) & 1) ^ 1, abortp)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_t = lane_base + kAccCols + sa * kAColsPerStage;
 #pragma unroll
-            for (int m = 0; m < 4; m++) {                 // 32 K per step -> 16 columns
+            for (int m = 0; m < 4; m++) {                 // 32 K per step -> 16 columns; step m is code field m
                 uint32_t r[16];
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
 #pragma unroll
                     for (int j2 = 0; j2 < 2; j2++) {
-                        // four codes (K offsets 16*j2 + 4t .. +3) in the low two bits of each byte
-                        const uint32_t y = ((j2 ? cur[m][t].y : cur[m][t].x) >> sh) & 0x03030303u;
+                        // four codes (K offsets 32m + 16*j2 + 4t .. +3) in the low two bits of each byte
+                        const uint32_t y = ((j2 ? cur[t].y : cur[t].x) >> (2 * m)) & 0x03030303u;
                         // selector nibbles 2c, 2c+1 per weight: one PRMT makes an FP16 pair {-s,0,+s}
                         r[8 * j2 + 2 * t] = prmt(tab_lo, tab_hi, y * 0x22u + 0x1010u);
                         r[8 * j2 + 2 * t + 1] = prmt(tab_lo, tab_hi, (y >> 16) * 0x22u + 0x1010u);
@@ -523,7 +518,7 @@ int launch_gemm_tcgen05(const half* A, const uint8_t* packed, half* C, int M, in
     a.N = N;
     a.K = K;
     a.groups = K / kStageK;
-    a.nrb = (N + kStRows - 1) / kStRows;
+    a.nrb = (N + kTileRows - 1) / kTileRows;
     a.err = err;
     a.ws = nullptr;
     a.counters = nullptr;

@@ -5,47 +5,53 @@
 // CUDA cores costs 3-5, so the +x/-x/0 selection runs on the tensor cores instead.
 // Weights are stored as 2-bit offset codes c = t + 1, sixteen to a word, arranged so
 // that ONE logic instruction, `word & (0x03030303 << 2f)`, is an A-operand register of
-// mma.sync.m16n8k32 (unsigned bytes c * 4^f for rows 16f..16f+15 of a 64-row
-// super-tile).  The B operand carries the activations; integer MMA keeps every group
-// sum exact; sum(t*x) = sum(c*x) - sum(x) with sum(x) made once per group when the
-// activations are staged; the factor 4^f is divided out in FP32 with the scale.
+// mma.sync.m16n8k32 (unsigned bytes c * 4^f of the 32 columns 32f..32f+31 of a 16-row x
+// 128-column tile).  The B operand carries the activations as small signed digits, and the
+// digits of the even steps (f = 0, 2) are stored multiplied by 4: then steps 0 and 1 both
+// carry the factor 4 and accumulate in one MMA chain, steps 2 and 3 both carry 64 and
+// accumulate in a second, and D_lo * 16 + D_hi = 64 * sum(c*x) exactly, in integers.
+// sum(t*x) = sum(c*x) - sum(x) with sum(x) made once per group when the activations are
+// staged; the factor 64 is divided out in FP32 with the scale.
 //
 //   FP16 activations: each scale group of 128 activations is converted once per CTA to
-//   block fixed point, q = rint(x * 2^(22-e)) with 2^e > max|x| of the group, stored
-//   as three BALANCED signed byte digits, q = d0 + 256*d1 + 65536*d2 with d in
-//   [-128,127] (the bytes of q + 0x808080, each xor 0x80).  A vector occupies three B
-//   columns [d0 d1 d2]; up to two vectors share one MMA (columns 0-2 and 4-6), up to
-//   four take two MMAs per operand register.  Every digit sum is exact in INT32 and is
-//   converted to FP32 once per group and row.  Rounding x to 23 bits below the group
+//   block fixed point, q = rint(x * 2^(22-e)) with 2^e > max|x| of the group, stored as
+//   four BALANCED base-64 digits, q = d0 + 64 d1 + 4096 d2 + 262144 d3 with d in [-32,31]
+//   (the 6-bit fields of q + 32*(1+64+64^2+64^3), each minus 32), so that a digit times 4
+//   still is a signed byte.  A vector occupies four B columns; two vectors share one MMA,
+//   up to four take two MMAs per operand register.  Every digit sum is exact in INT32 and
+//   is converted to FP32 once per group and row.  Rounding x to 23 bits below the group
 //   maximum is at the level of FP32 accumulation rounding itself.  A group that holds a
 //   NaN or an infinity makes its outputs NaN, as FP32 accumulation of x would.
-//   INT8 activations (ternary_gemv_int8 semantics): B is the int8 vector as is.
+//   INT8 activations (ternary_gemv_int8 semantics): the vector as two digit columns,
+//   x = lo + 16 hi with lo = x & 15 and hi = x >> 4; integer group sums stay exact.
 //
-// Work decomposition: the matrix is a linear array of super-tiles (64 rows x one scale
-// group, 2176 bytes; row-block major).  They are dealt to CTAs (one per SM) and, inside
-// a CTA, to 16 warps in contiguous, equal ranges, so K is split wherever rows alone
-// would not balance 148 SMs.  Weights arrive through ONE ring of R slots per CTA
-// (16-byte cp.async copies issued by all lanes of a warp, completion counted on one
-// mbarrier per slot, a super-tile per slot -- measured on this part, a ring fed by
-// cp.async.bulk tops out near 4 TB/s over the whole GPU whatever its depth, while
-// per-thread loads reach the full HBM rate): the j-th super-tile
-// of warp w has sequence number u = 16j + w and uses slot u mod R, so the ring is
-// shared evenly whatever R is, R is simply what the shared-memory budget allows (two
-// CTAs per SM: one computing, the next launch prefetching), and the first R are
-// requested at kernel start.  The warp that finishes sequence number u refills its
-// slot with u + R and publishes the slot's new use number in shared memory first: the
-// consumer of u + R (another warp) looks at that number before it waits on the slot's
-// mbarrier, because a parity wait on a barrier that is still one phase behind would
-// return at once.  Partial sums of a 64-row block are combined in a fixed order:
-// first over the warps of a CTA, then, for a block that spans several CTAs, by
-// whichever CTA arrives last, which adds the CTAs' records in CTA order.  Results
-// therefore do not depend on timing.
+// Work decomposition: the matrix is a linear array of tiles (16 rows x one scale group,
+// 544 bytes; row-block major).  They are dealt to CTAs (one per SM) and, inside a CTA, to
+// 16 warps in contiguous, equal ranges: whole 16-row blocks per CTA where that balances
+// the SMs (or where a CTA's share fits its ring anyway), otherwise K is split across
+// CTAs.  A warp walks its range in chunks of four tiles.  Weights arrive through a ring
+// of R slots per CTA (a chunk per slot; 16-byte cp.async copies issued by all lanes of a
+// warp, completion counted on one mbarrier per slot -- measured on this part, a ring fed
+// by cp.async.bulk tops out near 4 TB/s over the whole GPU whatever its depth, while
+// per-thread loads reach the full HBM rate).  R is what the shared-memory budget allows
+// (two CTAs per SM: one computing, the next launch prefetching); the slots are dealt to
+// the warps as private rings of depth R/16, the first R mod 16 warps one deeper, so every
+// slot is filled and emptied by one warp in program order (no cross-warp hand-over, no
+// parity wait on a barrier that is a phase behind) and a refill is one pointer increment.
+// The first `depth` chunks of every warp are requested at kernel start.  Partial sums of a
+// 16-row block are combined in a fixed order: first over the warps of a CTA, then, for a
+// block that spans several CTAs, by the LAST of those CTAs: the others store their sums
+// as 8-byte {value, flag} words (one store each, no fence, no atomic) and leave; the
+// last one polls -- bounded -- for the flags, adds the records in CTA order, writes the
+// outputs and clears the words for the next launch.  Results therefore do not depend on
+// timing.  (An arrival counter with fences on both sides costs four dependent round
+// trips to L2 per launch, about 3 us on this part; this costs one store and one load.)
 //
 // Launches carry the programmatic-dependent-launch attribute: the weight fetch is
 // issued before griddepcontrol.wait (weights are constants), activations are read
 // and outputs written after it, so a GEMV's weight stream starts while the kernel
-// before it in the stream drains.  Every mbarrier wait is bounded; a wait that
-// gives up records TLLM_ERR_TIMEOUT in a device flag and the kernel returns.
+// before it in the stream drains.  Every wait is bounded; a wait that gives up records
+// TLLM_ERR_TIMEOUT in a device flag and the kernel returns.
 #include <mutex>
 #include <unordered_map>
 
@@ -58,11 +64,16 @@ namespace tllm {
 constexpr int kWarpsLog2 = 4;
 constexpr int kWarps = 1 << kWarpsLog2;
 constexpr int kThreads = kWarps * 32;
-constexpr int kMaxSlots = 100;                        // ring slots per CTA, upper bound
 constexpr int kTickets = 16;                          // independent scratch regions
 constexpr int kMaxCtas = 256;
 constexpr int kMaxVec = 4;                            // vectors per weight pass
-constexpr int kRecFloats = kStRows * kMaxVec;         // one partial record: 64 rows x 4 vectors
+#ifndef TLLM_GEMV_SLOT_TILES
+#define TLLM_GEMV_SLOT_TILES 4
+#endif
+constexpr int kSlotTiles = TLLM_GEMV_SLOT_TILES;      // tiles per chunk = per ring slot
+constexpr int kSlotBytes = kSlotTiles * kTileBytes;   // 2176
+constexpr int kMaxSlots = 400 / kSlotTiles;           // ring slots per CTA, upper bound
+constexpr int kRecFloats = kTileRows * kMaxVec;       // one partial record: 16 rows x 4 vectors
 constexpr int kMaxPeers = TLLM_MAX_PEERS;
 // Dynamic shared memory of one CTA when two are to share an SM (228 KB per SM, 1 KB
 // reserved per resident CTA).
@@ -71,13 +82,18 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 #endif
 constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
 constexpr size_t kMaxSmemBytes = 226 * 1024;      // dynamic part; the kernel also has a few static bytes
-// L2 prefetch at kernel start of what a warp will stream beyond its first ring fill, in bytes
-// per warp (0 = off).  The fill itself is bounded by shared memory; this lets the HBM stream
-// of a launch go on into the 126 MB L2 while the launch still waits for the kernel before it.
-#ifndef TLLM_GEMV_L2_PREFETCH_BYTES
-#define TLLM_GEMV_L2_PREFETCH_BYTES 0
+// How far beyond the ring a warp asks for its weights to be brought into L2, in chunks (0 = off).
+// The ring is bounded by shared memory: 63 KB in flight per SM at the 2 us an HBM access takes
+// under load is 33 GB/s per SM, three quarters of the HBM rate.  The 126 MB L2 is the buffer that
+// decouples the HBM stream from the chain of dependent launches: with this set, each warp prefetches (one
+// prefetch.global.L2 per 128-byte line, no shared memory, no registers) the chunks it will copy
+// into the ring a few iterations later, starting in the prologue -- that is, while the kernel
+// in front of this one still runs -- so the ring's copies hit L2.  (cp.async.bulk.prefetch.L2 was
+// measured first and did not help: like the bulk copy itself it is bound by its own engine.)
+#ifndef TLLM_GEMV_L2_AHEAD_CHUNKS
+#define TLLM_GEMV_L2_AHEAD_CHUNKS 0
 #endif
-constexpr int kL2PrefetchSt = TLLM_GEMV_L2_PREFETCH_BYTES / kStBytes;
+constexpr int kL2Ahead = TLLM_GEMV_L2_AHEAD_CHUNKS;
 
 // kI8Norm / kI8Silu / kI8Quant: INT8 arithmetic like kI8, but the activation vector is
 // produced inside the kernel's staging phase from FP16 inputs (stage_x_fused below).
@@ -105,23 +121,22 @@ struct GemvArgs {
     int nseg;
     int seg_row[TLLM_MAX_FUSED + 1];
     half* seg_y[TLLM_MAX_FUSED];
-    int rows, cols, groups; // groups = cols / 128 = super-tiles per row block
+    int rows, cols, groups; // groups = cols / 128 = tiles per row block
     int batch;              // vectors handled by this launch (1..4, FP16 modes)
     int part_q, part_r;     // items = gridDim.x * part_q + part_r; CTA c owns q (+1 if c < r) items
-    int aligned;            // 1: items are whole row blocks (no block spans two CTAs); 0: items are super-tiles
+    int aligned;            // 1: items are whole row blocks (no block spans two CTAs); 0: items are tiles
     int late_release;       // 1: the next kernel in the stream is released after this kernel's own dependency
                             //    wait instead of at its start (see release_rule)
     int ring_slots;         // R
-    int l2_prefetch;        // 1: a warp asks for (part of) its super-tiles beyond the first ring fill to be
-                            //    brought into L2 at kernel start
-    int x_local;            // FP16 modes, CTAs with fewer super-tiles than a row has groups: a CTA stages only
-                            // the groups it walks (a cyclic run starting at its first super-tile's group)
+    int l2_prefetch;        // 1: warps prefetch into L2 the chunks beyond what the ring holds
+    int x_local;            // FP16 modes, CTAs with fewer tiles than a row has groups: a CTA stages only
+                            // the groups it walks (a cyclic run starting at its first tile's group)
     uint2* ws;              // [gridDim.x][2][ws_stride / 2] partial records {value, flag} of this ticket,
                             // all zero between launches
     int ws_stride;          // words per CTA in ws (two records)
     int* err;               // device error flag (0 = none)
     // shared memory carve-up (byte offsets); the staged activations start at 0
-    int off_xcst, off_part, off_ring, off_bar, off_gen;
+    int off_xcst, off_part, off_mask, off_ring, off_bar;
     // Fused all-reduce over peer memory (row-parallel shards of a tensor-parallel layer);
     // ar_world == 0 switches it off.  Every rank runs the same launch on its own shard.
     int ar_world, ar_rank, ar_rows_max;
@@ -152,7 +167,7 @@ static inline int release_rule(int rows, int cols)
 // Diagnostic build only (python -m ternary_llm_b200.build --timeline, which defines
 // TLLM_TIMELINE and writes libtllm_b200_timeline.so): thread 0 of every CTA of every GEMV launch
 // records the GPU's nanosecond timer at seven points -- kernel entry, first ring fill issued,
-// stream-order wait over, activations staged, last super-tile done, partial sums exchanged
+// stream-order wait over, activations staged, last tile done, partial sums exchanged
 // inside the CTA, outputs written -- into a ring of the last 8 launches, read back by
 // tllm_b200_timeline_read.  The shipped library contains none of this.
 #ifdef TLLM_TIMELINE
@@ -194,20 +209,48 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
         if (mbar_try(bar, parity)) return true;
     return false;
 }
-// One super-tile global -> shared by the 32 lanes of a warp: 136 copies of 16 bytes (lanes 0..7
-// issue a fifth one), then each lane makes the slot's mbarrier count its copies: the barrier
-// (initialised to 32 arrivals) completes its phase when every lane's copies have landed.
-__device__ __forceinline__ void fill_slot(uint32_t dst, const uint8_t* src, uint32_t bar, int lane)
+// One chunk (n16 pieces of 16 bytes: 34 per tile) global -> shared by the 32 lanes of a warp,
+// then each lane makes the slot's mbarrier count its copies: the barrier (initialised to 32
+// arrivals) completes its phase when every lane's copies have landed.
+__device__ __forceinline__ void fill_slot(uint32_t d, const uint8_t* s, uint32_t bar, int lane, int n16)
 {
+    // d, s: this lane's first piece (slot or chunk start + 16 * lane)
+    constexpr int kFull = kSlotBytes / 16;                 // pieces of a whole chunk
+    constexpr int kRounds = (kFull + 31) / 32;
+    if (n16 == kFull) {                                    // whole chunk: no bounds test but in the last round
 #pragma unroll
-    for (int i = 0; i < 4; i++)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                     ::"r"(dst + (uint32_t)(i * 32 + lane) * 16u), "l"(src + (size_t)(i * 32 + lane) * 16) : "memory");
-    if (lane < kStBytes / 16 - 128)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                     ::"r"(dst + (uint32_t)(128 + lane) * 16u), "l"(src + (size_t)(128 + lane) * 16) : "memory");
+        for (int i = 0; i < kRounds; i++)
+            if ((i + 1) * 32 <= kFull || i * 32 + lane < kFull)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i * 512u), "l"(s + i * 512) : "memory");
+    } else {
+#pragma unroll
+        for (int i = 0; i < kRounds; i++)
+            if (i * 32 + lane < n16)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i * 512u), "l"(s + i * 512) : "memory");
+    }
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+
+// Shared-memory loads by 32-bit shared address.
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<half2*>(&v); }
 
 // D = A.B (+ D unless FIRST), A unsigned bytes (offset codes), B signed bytes.  The zero
 // accumulator of the first step is passed as immediates so that no register is cleared.
@@ -234,31 +277,52 @@ __device__ __forceinline__ int part_of(int u, int q, int r)
     const int big = r * (q + 1);
     return (u < big) ? (int)((unsigned)u / (unsigned)(q + 1)) : r + (int)((unsigned)(u - big) / (unsigned)q);
 }
-// The n super-tiles of a CTA over its warps: warp w owns [w*n/kWarps, (w+1)*n/kWarps).
-__device__ __forceinline__ int warp_start(int w, int n) { return (w * n) >> kWarpsLog2; }
-__device__ __forceinline__ int warp_of(int i, int n) { return (int)((unsigned)((i + 1) * kWarps - 1) / (unsigned)n); }
+// The n tiles of a CTA over its warps: warp w owns [warp_start(w), warp_start(w + 1)), about
+// n/kWarps tiles each; with eight or more tiles per warp the starts are rounded down to whole
+// chunks, so that chunks and row blocks (of a multiple of four groups) stay aligned.
+__device__ __forceinline__ int warp_start(int w, int n)
+{
+    const int s = (w * n) >> kWarpsLog2;
+    return (n >= 8 * kWarps && w < kWarps) ? (s & ~(kSlotTiles - 1)) : s;
+}
 
 // ---------------------------------------------------------------------------
 // Activation staging
 // ---------------------------------------------------------------------------
 // Shared-memory layout of the staged activations, FP16 modes.  NB = MMA column blocks
 // (n8) per operand register, NV = vectors per block (1 or 2).  Vector v lives in block
-// v / NV... precisely: block beta = v >> 1 when NV == 2 (beta = 0 when NV == 1), column
-// group vl = v & 1, so that the digit d of vector v is B column 4*vl + d of block beta.
-//   xdig : uint4 [groups][2 step pairs][NB][NV*3 columns][4 lanes t]
+// beta = v >> 1 when NV == 2 (beta = 0 when NV == 1), column group vl = v & 1, so that the
+// digit d of vector v is B column 4*vl + d of block beta.
+//   xdig : uint4 [groups][2 step pairs][NB][NV*4 columns][4 lanes t]
 //          the four words of an entry are (b0,b1) of k32 step 2p and (b0,b1) of step 2p+1 of
-//          MMA lane (column, t), so one 128-bit shared load feeds two k32 steps;
-//   xcst : uint4 [groups][NB*NV]  = {f, S01, 65536 f, S2}: f = 2^(e-22) of the group (NaN for a
-//          group that holds a non-finite value), S01 = sum(d0 + 256 d1), S2 = sum(d2).
-// The digit word of four consecutive activations: byte c of q + 0x808080, xor 0x80.
-__device__ __forceinline__ void quad_digits(uint32_t q0, uint32_t q1, uint32_t q2, uint32_t q3,
-                                            uint32_t& w0, uint32_t& w1, uint32_t& w2)
+//          MMA lane (column, t), so one 128-bit shared load feeds two k32 steps; the words of
+//          the even step hold 4 x digit;
+//   xcst : uint4 [groups][NB*NV]  = {f/64, 64 S_lo, 64 f, 64 S_hi}: f = 2^(e-22) of the group (NaN for
+//          a group that holds a non-finite value), S_lo = sum(d0 + 64 d1), S_hi = sum(d2 + 64 d3);
+//          lanes of the columns (d0,d1) use the first pair, lanes of (d2,d3) -- worth 4096 -- the
+//          second; the 64 is the factor the combined MMA results carry.
+constexpr uint32_t kDigitOffset = 32u * (1u + 64u + 4096u + 262144u);    // 8521760
+
+// Digit words of four consecutive activations u0..u3 (each q + kDigitOffset, 24 bits): byte k
+// of word i is the 6-bit digit i of activation k as a signed byte, shifted left by `sh` (0 or
+// 2: the even k32 steps carry 4 x digit).  The bytes of the four values are transposed first,
+// so that every mask and shift then works on four activations at once.
+__device__ __forceinline__ void quad_digits(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t u3, uint32_t sh, uint32_t bias,
+                                            uint32_t (&w)[4])
 {
-    const uint32_t u = __byte_perm(q0, q1, 0x5140), v = __byte_perm(q2, q3, 0x5140);
-    const uint32_t r = __byte_perm(q0, q1, 0x0062), s = __byte_perm(q2, q3, 0x0062);
-    w0 = __byte_perm(u, v, 0x5410) ^ 0x80808080u;
-    w1 = __byte_perm(u, v, 0x7632) ^ 0x80808080u;
-    w2 = __byte_perm(r, s, 0x5410) ^ 0x80808080u;
+    const uint32_t a = __byte_perm(u0, u1, 0x5140), b = __byte_perm(u2, u3, 0x5140);
+    const uint32_t c = __byte_perm(u0, u1, 0x0062), d = __byte_perm(u2, u3, 0x0062);
+    const uint32_t t0 = __byte_perm(a, b, 0x5410);          // bits  0..7  of the four values
+    const uint32_t t1 = __byte_perm(a, b, 0x7632);          // bits  8..15
+    const uint32_t t2 = __byte_perm(c, d, 0x5410);          // bits 16..23
+    uint32_t v[4];
+    v[0] = t0 & 0x3f3f3f3fu;
+    v[1] = ((t0 >> 6) & 0x03030303u) | ((t1 << 2) & 0x3c3c3c3cu);
+    v[2] = ((t1 >> 4) & 0x0f0f0f0fu) | ((t2 << 4) & 0x30303030u);
+    v[3] = (t2 >> 2) & 0x3f3f3f3fu;
+    // field v in 0..63 -> (v - 32) or 4 (v - 32) as a signed byte: bias = 0x60606060 or 0
+#pragma unroll
+    for (int i = 0; i < 4; i++) w[i] = ((v[i] << sh) + bias) ^ 0x80808080u;
 }
 
 // Each thread converts 8 consecutive activations (one 128-bit load); the 16 lanes of a
@@ -271,91 +335,107 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
 {
     constexpr int NVT = NB * NV;
     const int per_vec = gcount << 4;               // 8-element items per vector (16 per group)
-    const int items = per_vec * batch;
+    const int items = per_vec * batch;             // a multiple of 16: a half-warp is all in or all out
     const int l16 = tid & 15;
     // vectors of the last block that do not exist: their constants are zero, so whatever the
     // MMA makes of their (unwritten) digit columns never reaches a finite-times-NaN product
-    for (int i = tid; i < gcount * (NVT - batch); i += kThreads) {
-        const int g = i / (NVT - batch), v = batch + i % (NVT - batch);
-        xcst[g * NVT + v] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    for (int base = 0; base < items; base += kThreads) {
-        const int item = base + tid;
-        const bool valid = item < items;           // uniform per half-warp
-        const int ic = valid ? item : 0;
-        const int b = (int)((unsigned)ic / (unsigned)per_vec);
-        const int el = ic - b * per_vec;           // item index inside the staged run
-        const int g = el >> 4;                     // staged group number
-        int gg = g0 + g;                           // its group in the vector
-        if (gg >= groups) gg -= groups;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + (el & 15));
-        float f[8];
-        {
-            const float2 f0 = __half22float2(*reinterpret_cast<const half2*>(&raw.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const half2*>(&raw.y));
-            const float2 f2 = __half22float2(*reinterpret_cast<const half2*>(&raw.z));
-            const float2 f3 = __half22float2(*reinterpret_cast<const half2*>(&raw.w));
-            f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y;
-            f[4] = f2.x; f[5] = f2.y; f[6] = f3.x; f[7] = f3.y;
+    if (NVT > 1)
+        for (int i = tid; i < gcount * (NVT - batch); i += kThreads) {
+            const int g = i / (NVT - batch), v = batch + i % (NVT - batch);
+            xcst[g * NVT + v] = make_uint4(0u, 0u, 0u, 0u);
         }
-        // largest magnitude as a bit pattern: orders finite values, infinities and NaNs alike
-        uint32_t mb = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) mb = max(mb, __float_as_uint(f[i]) & 0x7fffffffu);
+    // elements 8*l16 .. 8*l16+7 of a group: k32 step m = l16 / 4, half j2 = (l16 / 2) & 1,
+    // MMA lanes t = 2*(l16 & 1) and the next one; the even steps carry 4 x digit
+    const int m = l16 >> 2, j2 = (l16 >> 1) & 1, t0 = 2 * (l16 & 1);
+    const uint32_t sh = (m & 1) ? 0u : 2u, bias = (m & 1) ? 0x60606060u : 0u;
+    const int lane_off = t0 * 4 + (m & 1) * 2 + j2 + (m >> 1) * (NB * NV * 64);   // words, inside a group's entry
+    auto fetch = [&](int item) {
+        const int b = (NVT == 1) ? 0 : (int)((unsigned)item / (unsigned)per_vec);
+        const int el = item - b * per_vec;
+        int gg = g0 + (el >> 4);
+        if (gg >= groups) gg -= groups;
+        return __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16);
+    };
+    int item = tid;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (item < items) raw = fetch(item);
+    for (; (item & ~31) < items; item += kThreads) {          // warp-uniform: the shuffles need every lane
+        const bool valid = item < items;
+        const uint4 cur = raw;
+        if (item + kThreads < items) raw = fetch(item + kThreads);      // in flight during this item's arithmetic
+        const int b = (NVT == 1 || !valid) ? 0 : (int)((unsigned)item / (unsigned)per_vec);
+        const int g = ((valid ? item : 0) - b * per_vec) >> 4;          // staged group number
+        // largest magnitude of the group as an FP16 bit pattern: orders finite values,
+        // infinities and NaNs alike
+        uint32_t mb = __vmaxu2(__vmaxu2(cur.x & 0x7fff7fffu, cur.y & 0x7fff7fffu),
+                               __vmaxu2(cur.z & 0x7fff7fffu, cur.w & 0x7fff7fffu));
+        mb = max(mb & 0xffffu, mb >> 16);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
-        const bool finite = mb < 0x7f800000u;
-        // 2^e > max|x|; FP16 inputs keep e within [-23, 16]
-        const int e = max((int)(mb >> 23) - 126, -24);
+        const bool finite = mb < 0x7c00u;
         const bool live = finite && mb != 0u;
+        // 2^e > max|x| with e = E - 14 (E the biased FP16 exponent; subnormals count as E = 1)
+        const int e = (int)max(mb >> 10, 1u) - 14;
         const float up = live ? __uint_as_float((uint32_t)(22 - e + 127) << 23) : 0.f;
         const float dn = finite ? (mb != 0u ? __uint_as_float((uint32_t)(e - 22 + 127) << 23) : 0.f)
                                 : __uint_as_float(0x7fc00000u);
-        uint32_t q[8];
-        int sq = 0, s2 = 0;
+        // q = rint(x * up) through the mantissa of x * up + 1.5 * 2^23 (one rounding, to nearest even,
+        // |q| < 2^22), and u = q + kDigitOffset
+        uint32_t u[8];
+        {
+            const uint32_t rw[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int qi = live ? __float2int_rn(f[i] * up) : 0;
-            q[i] = (uint32_t)(qi + 0x808080);
-            sq += qi;
-            s2 += (int)((q[i] >> 16) & 0xffu) - 128;
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rw[i]));
+                u[2 * i] = __float_as_uint(fmaf(f.x, up, 12582912.0f)) - 0x4b400000u + kDigitOffset;
+                u[2 * i + 1] = __float_as_uint(fmaf(f.y, up, 12582912.0f)) - 0x4b400000u + kDigitOffset;
+            }
         }
+        uint32_t w[2][4];
+        quad_digits(u[0], u[1], u[2], u[3], sh, bias, w[0]);
+        quad_digits(u[4], u[5], u[6], u[7], sh, bias, w[1]);
+        // digit sums of the group (times 4 on the even steps): low pair d0 + 64 d1, high pair d2 + 64 d3
+        int sd[4];
+#pragma unroll
+        for (int d = 0; d < 4; d++) sd[d] = __dp4a((int)w[1][d], 0x01010101, __dp4a((int)w[0][d], 0x01010101, 0));
+        int slo = (sd[0] + 64 * sd[1]) >> sh, shi = (sd[2] + 64 * sd[3]) >> sh;
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
-            sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+            slo += __shfl_xor_sync(0xffffffffu, slo, o);
+            shi += __shfl_xor_sync(0xffffffffu, shi, o);
         }
-        uint32_t w[2][3];
-        quad_digits(q[0], q[1], q[2], q[3], w[0][0], w[0][1], w[0][2]);
-        quad_digits(q[4], q[5], q[6], q[7], w[1][0], w[1][1], w[1][2]);
         if (valid) {
-            // elements 8*l16 .. 8*l16+7 of the group: k32 step m = l16 / 4, half j2 = (l16 / 2) & 1,
-            // MMA lanes t = 2*(l16 & 1) and the next one
-            const int m = l16 >> 2, j2 = (l16 >> 1) & 1, t0 = 2 * (l16 & 1);
             const int beta = (NV == 2) ? (b >> 1) : 0, vl = (NV == 2) ? (b & 1) : 0;
-            uint32_t* p = xdig + ((((g * 2 + (m >> 1)) * NB + beta) * (NV * 3) + vl * 3) * 4 + t0) * 4 + (m & 1) * 2 + j2;
+            uint32_t* p = xdig + ((g * 2 * NB + beta) * (NV * 4) + vl * 4) * 16 + lane_off;
 #pragma unroll
             for (int h = 0; h < 2; h++)             // second quad: next lane t
 #pragma unroll
-                for (int d = 0; d < 3; d++) p[(d * 4 + h) * 4] = w[h][d];
-            if (l16 == 0) {
-                const float dn16 = dn * 65536.0f;
-                xcst[g * NVT + b] = make_uint4(__float_as_uint(dn), (uint32_t)(sq - 65536 * s2),
-                                               __float_as_uint(dn16), (uint32_t)s2);
-            }
+                for (int d = 0; d < 4; d++) p[(d * 4 + h) * 4] = w[h][d];
+            if (l16 == 0)
+                xcst[g * NVT + b] = make_uint4(__float_as_uint(dn * 0.015625f), (uint32_t)(slo * 64),
+                                               __float_as_uint(dn * 64.0f), (uint32_t)(shi * 64));
         }
     }
 }
 
-// INT8 activations in shared memory are permuted so that the four B words a lane needs for
-// two k32 steps are one 128-bit entry: uint4 [groups][2 step pairs][4 lanes t], words
-// (b0,b1) of step 2p and (b0,b1) of step 2p+1.  Original word w of the vector (four
-// consecutive activations) goes to this 32-bit slot.
-__device__ __forceinline__ int int8_word_slot(int w)
+// INT8 activations in shared memory: two digit columns, x = lo + 16 hi with lo = x & 15 (0..15)
+// and hi = x >> 4 (-8..7), laid out like the FP16 digits: uint4 [groups][2 step pairs][2 columns]
+// [4 lanes t], words (b0,b1) of step 2p and (b0,b1) of step 2p+1, the even step times 4.
+// Stores the two digit words of original word w of the vector (four consecutive activations).
+__device__ __forceinline__ void store_i8_word(uint32_t* xq, int w, uint32_t xw)
 {
     const int g = w >> 5, r = w & 31;
     const int m = r >> 3, j2 = (r >> 2) & 1, t = r & 3;
-    return (g << 5) + ((((m >> 1) << 2) + t) << 2) + ((m & 1) << 1) + j2;
+    uint32_t lo = xw & 0x0f0f0f0fu;
+    const uint32_t h = (xw >> 4) & 0x0f0f0f0fu;
+    uint32_t hi = h | ((h & 0x08080808u) * 0x1eu);           // sign-extend each nibble to a byte
+    if ((m & 1) == 0) {
+        lo <<= 2;
+        hi = (hi << 2) & 0xfcfcfcfcu;
+    }
+    uint32_t* p = xq + (((g * 2 + (m >> 1)) * 2) * 4 + t) * 4 + (m & 1) * 2 + j2;
+    p[0] = lo;
+    p[16] = hi;
 }
 
 // Block-wide reductions over the CTA's kWarps warps; `red` is 33 floats of shared memory.
@@ -395,7 +475,8 @@ __device__ __forceinline__ float cta_max(float v, float* red, int tid)
 // Sum of the four signed bytes of a word.
 __device__ __forceinline__ int byte_sum(uint32_t w) { return __dp4a((int)w, 0x01010101, 0); }
 
-// INT8 vector from global memory: permuted copy plus the per-group sums sx[groups].
+// INT8 vector from global memory: its digit columns plus 64 x the per-group sums, sx[groups] (64
+// is the factor the combined MMA results carry).
 __device__ __forceinline__ void stage_x_i8(const int8_t* __restrict__ x, int cols, uint32_t* xq, int* sx, int tid)
 {
     const int n16 = cols >> 4;                     // 16-byte items (8 per group)
@@ -409,13 +490,11 @@ __device__ __forceinline__ void stage_x_i8(const int8_t* __restrict__ x, int col
 #pragma unroll
         for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (valid) {
-            // words 4i .. 4i+3 share the k32 step and the half, their lanes are t = 0..3
-            const int s0 = int8_word_slot(4 * i);
-            xq[s0] = v.x;
-            xq[s0 + 4] = v.y;
-            xq[s0 + 8] = v.z;
-            xq[s0 + 12] = v.w;
-            if ((i & 7) == 0) sx[i >> 3] = s;
+            store_i8_word(xq, 4 * i, v.x);
+            store_i8_word(xq, 4 * i + 1, v.y);
+            store_i8_word(xq, 4 * i + 2, v.z);
+            store_i8_word(xq, 4 * i + 3, v.w);
+            if ((i & 7) == 0) sx[i >> 3] = s * 64;
         }
     }
 }
@@ -505,9 +584,9 @@ __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, uint32_t* xq, 
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (valid) {
-            xq[int8_word_slot(2 * i)] = w[0];
-            xq[int8_word_slot(2 * i + 1)] = w[1];
-            if ((i & 15) == 0) sx[i >> 4] = s;
+            store_i8_word(xq, 2 * i, w[0]);
+            store_i8_word(xq, 2 * i + 1, w[1]);
+            if ((i & 15) == 0) sx[i >> 4] = s * 64;
         }
     }
     return (absmax > 0.f) ? (absmax / 127.0f) : 1.0f;
@@ -528,7 +607,7 @@ __device__ __forceinline__ half* out_ptr(const GemvArgs& a, int b, int r)
 // Kernel
 // ---------------------------------------------------------------------------
 template <int MODE, int NB, int NV, bool AR>
-__global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs a)
+__global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_constant__ GemvArgs a)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu || MODE == kI8Quant);
@@ -547,44 +626,60 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     if (tracing) ts[0] = globaltimer();
     TL_BEGIN();
     TL(0);
+    // Kernel parameters sit in a constant bank that is new with every launch: the first read of
+    // each of its cache lines goes out to memory.  Every line is read once here, where the
+    // latency hides behind the previous kernel, and the part of the kernel that runs after the
+    // last tile -- on the critical path of the stream -- reads the copy in shared memory.
+    __shared__ __align__(16) uint32_t sargs[(sizeof(GemvArgs) + 3) / 4];
+    if (tid < (int)(sizeof(GemvArgs) / 4)) sargs[tid] = reinterpret_cast<const uint32_t*>(&a)[tid];
     const int G = a.groups, R = a.ring_slots;
-    const int per = a.aligned ? G : 1;                                     // super-tiles per partition item
-    const int t0 = part_start(blockIdx.x, a.part_q, a.part_r) * per;      // first super-tile of this CTA
-    const int n = (a.part_q + ((int)blockIdx.x < a.part_r ? 1 : 0)) * per; // super-tiles of this CTA
-    const int rb_first = (int)((unsigned)t0 / (unsigned)G);
-    const int rb_last = (int)((unsigned)(t0 + n - 1) / (unsigned)G);
+    const int per = a.aligned ? G : 1;                                     // tiles per partition item
+    const int t0 = part_start(blockIdx.x, a.part_q, a.part_r) * per;      // first tile of this CTA
+    const int n = (a.part_q + ((int)blockIdx.x < a.part_r ? 1 : 0)) * per; // tiles of this CTA
+    // first and last row block this CTA holds tiles of (whole row blocks: no division needed)
+    const int rb_first = a.aligned ? part_start(blockIdx.x, a.part_q, a.part_r) : (int)((unsigned)t0 / (unsigned)G);
+    const int rb_last = a.aligned ? rb_first + a.part_q - ((int)blockIdx.x < a.part_r ? 0 : 1)
+                                  : (int)((unsigned)(t0 + n - 1) / (unsigned)G);
 
     uint32_t* xstage = reinterpret_cast<uint32_t*>(smem);              // digits, or the int8 vector
     uint4* xcst = reinterpret_cast<uint4*>(smem + a.off_xcst);         // FP16 modes: group constants
-    int* sx = reinterpret_cast<int*>(smem + a.off_xcst);               // INT8 modes: group sums
-    float* part = reinterpret_cast<float*>(smem + a.off_part);         // [segment][64 rows][NVT]
+    int* sx = reinterpret_cast<int*>(smem + a.off_xcst);               // INT8 modes: 64 x group sums
+    float* part = reinterpret_cast<float*>(smem + a.off_part);         // [segment][16 rows][NVT]
+    uint32_t* contrib = reinterpret_cast<uint32_t*>(smem + a.off_mask);    // per row block of this CTA: the warps that hold sums of it
     const uint32_t ring = smem_addr(smem + a.off_ring);
-    const uint8_t* ring_p = smem + a.off_ring;
     const uint32_t bar = smem_addr(smem + a.off_bar);
-    volatile uint32_t* gen = reinterpret_cast<volatile uint32_t*>(smem + a.off_gen);   // use number of each slot
 
-    // ---- this warp's super-tile range and the first ring fill ---------------------
+    // ---- this warp's tile range, in chunks of four, and the first ring fill ------------
     const int w0 = t0 + warp_start(warp, n), w1 = t0 + warp_start(warp + 1, n);
     const int nw = w1 - w0;                                  // may be 0 for tiny problems
+    const int nchunks = (nw + kSlotTiles - 1) / kSlotTiles;
+    // this warp's private ring: slots s0 .. s0 + depth - 1 of the CTA's R
+    const int depth = (R >> kWarpsLog2) + (warp < (R & (kWarps - 1)) ? 1 : 0);
+    const int s0 = warp * (R >> kWarpsLog2) + min(warp, R & (kWarps - 1));
+    const uint32_t ring_w = ring + (uint32_t)s0 * kSlotBytes + (uint32_t)lane * 16u;   // this lane's first piece of slot 0
+    const uint32_t bar_w = bar + (uint32_t)s0 * 8u;
     if (lane == 0) {
-        for (int s = warp; s < R; s += kWarps) {
-            mbar_init(bar + s * 8, 32);
-            gen[s] = 0u;
-        }
+        for (int k = 0; k < depth; k++) mbar_init(bar_w + k * 8, 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    {
-        // sequence numbers 16j + warp < R go to slots of the same number
-        int j = 0;
-        for (int s = warp; s < R && j < nw; j++, s += kWarps)
-            fill_slot(ring + s * kStBytes, a.packed + (size_t)(w0 + j) * kStBytes, bar + s * 8, lane);
-        if (kL2PrefetchSt > 0 && a.l2_prefetch && j < nw && lane == 0) {
-            const uint32_t bytes = (uint32_t)min(nw - j, kL2PrefetchSt) * kStBytes;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
-                         ::"l"(a.packed + (size_t)(w0 + j) * kStBytes), "r"(bytes) : "memory");
-        }
-    }
+    // pieces of 16 bytes in chunk c of this warp's range
+    auto pieces = [&](int c) { return min(kSlotTiles, nw - c * kSlotTiles) * (kTileBytes / 16); };
+    const uint8_t* src_lane = a.packed + (size_t)w0 * kTileBytes + (size_t)lane * 16;
+    // chunk `cidx` of this warp's range -> L2, one 128-byte line per lane
+    auto l2_chunk = [&](int cidx) {
+        const uint8_t* p0 = a.packed + (size_t)(w0 + cidx * kSlotTiles) * kTileBytes;
+        const uint32_t bytes = (uint32_t)min(kSlotTiles, nw - cidx * kSlotTiles) * kTileBytes;
+        const uintptr_t first = reinterpret_cast<uintptr_t>(p0) & ~(uintptr_t)127;
+        const uint32_t lines = (uint32_t)((reinterpret_cast<uintptr_t>(p0) + bytes - first + 127) >> 7);
+        if ((uint32_t)lane < lines) asm volatile("prefetch.global.L2 [%0];" ::"l"(first + (uintptr_t)lane * 128) : "memory");
+    };
+    const int cinit = min(depth, nchunks);                   // chunks of the first ring fill
+    for (int c = 0; c < cinit; c++)
+        fill_slot(ring_w + c * kSlotBytes, src_lane + (size_t)c * kSlotBytes, bar_w + c * 8, lane, pieces(c));
+    if (kL2Ahead > 0 && a.l2_prefetch)
+        for (int c = cinit; c < min(nchunks, cinit + kL2Ahead); c++) l2_chunk(c);
+    const uint8_t* src_next = src_lane + (size_t)cinit * kSlotBytes;      // the next chunk to request
     __syncwarp();
     TL(1);
 
@@ -598,6 +693,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
     unsigned ar_epoch_prev = 0;
     if (kAr && a.ar_world > 0) ar_epoch_prev = __ldcg(a.ar_epoch + blockIdx.x);
 
+    for (int i = tid; i <= rb_last - rb_first; i += kThreads) contrib[i] = 0u;    // set in flush(), after the barrier below
     float fused_scale = 1.0f;
     if (FUSEDX) {
         fused_scale = stage_x_fused<MODE>(a, xstage, sx, reinterpret_cast<half*>(smem + a.off_xtmp),
@@ -614,146 +710,158 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
 
     // ---- per-lane constants ------------------------------------------------------
     const int t = lane & 3, gq = lane >> 2;
-    // FP16: this lane's accumulator columns 2t, 2t+1 are digits (0,1) of vector t/2 of the
-    // block when t is even, digit 2 (and an unused column) when t is odd
-    const int mulA = (t & 1) ? 0 : 256;
-    // B operand entry of this lane: column gq -> (vector gq / 4 of the block, digit gq % 4);
-    // lanes of columns that carry nothing read a neighbour's entry, their products are unused
-    const int bcol = min(gq >> 2, NV - 1) * 3 + min(gq & 3, 2);
-    const uint4* xb_lane = reinterpret_cast<const uint4*>(xstage) + (I8 ? t : bcol * 4 + t);
-    constexpr int kXbStride = I8 ? 4 : NV * 12;                 // entries per (group, step pair, block)
+    // This lane's accumulator columns 2t, 2t+1 are two digits of one vector.  FP16: digits (0,1)
+    // of vector t/2 of the block when t is even, digits (2,3) -- worth 4096 -- when t is odd; the
+    // second digit of a pair counts 64.  INT8: (lo, hi) in columns 0, 1, the second counts 16.
+    constexpr int kMulA = I8 ? 16 : 64;
+    // B operand entry of this lane: column gq -> FP16 (vector gq / 4 of the block, digit gq % 4),
+    // INT8 digit gq; lanes of columns that carry nothing read a neighbour's entry, their products
+    // are unused.  Shared-memory addresses are kept as 32-bit numbers.
+    const int bcol = I8 ? min(gq, 1) : (min(gq >> 2, NV - 1) * 4 + (gq & 3));
+    constexpr int kXbStride = I8 ? 8 : NV * 16;                 // entries per (group, step pair, block)
+    constexpr uint32_t kXgBytes = 2u * NB * kXbStride * 16u;    // staged bytes per group
+    const uint32_t xb_addr = smem_addr(xstage) + (uint32_t)(bcol * 4 + t) * 16u;
+    // group constants of this lane: FP16 {factor, offset} pair (first pair for even t, second for odd)
+    const uint32_t xc_addr = smem_addr(smem + a.off_xcst) + (I8 ? 0u : (uint32_t)(t & 1) * 8u);
+    const uint32_t sc_off = kTileCodeBytes + (uint32_t)gq * 4u;      // this lane's two scales inside a tile
+    const bool xloc = !I8 && a.x_local;
 
-    // ---- main loop: this warp's super-tiles, one ring slot each --------------------
-    int rb = (int)((unsigned)w0 / (unsigned)G);
-    int g = w0 - rb * G;
-    int gx_local = w0 - t0;                  // FP16 modes with x_local: where group g's activations were staged
-    int seg = (rb - rb_first) + warp;        // partial-sum slot: unique per (warp, row block), ascending
-    float acc[NB][4][2];                     // [block][field f][row half h]: rows 16f + gq + 8h of row block rb
+    // ---- main loop: this warp's tiles, four per ring slot ----------------------------
+    const int rb0 = (int)((unsigned)w0 / (unsigned)G);
+    int g = w0 - rb0 * G;                    // group (tile inside the row block) of the next tile
+    int gxi = xloc ? (w0 - t0) : g;          // where that group's activations were staged
+    int rbr = rb0 - rb_first;                // row block, relative to the CTA's first
+    float acc[NB][2];                        // [block][row half h]: rows gq + 8h of the row block
 #pragma unroll
-    for (int b = 0; b < NB; b++)
-#pragma unroll
-        for (int f = 0; f < 4; f++) acc[b][f][0] = acc[b][f][1] = 0.f;
-    bool dirty = false, ok = true;
+    for (int b = 0; b < NB; b++) acc[b][0] = acc[b][1] = 0.f;
+    bool ok = true;
 
+    // sums of the tiles walked since the last flush -> this warp's record of the row block
     auto flush = [&]() {
-        float* pu = part + (size_t)seg * (kStRows * NVT);
+        float* pu = part + (size_t)(rbr + warp) * (kTileRows * NVT);     // unique per (warp, row block), ascending
+        if (lane == 0) atomicOr(contrib + rbr, 1u << warp);
 #pragma unroll
         for (int b = 0; b < NB; b++)
 #pragma unroll
-            for (int f = 0; f < 4; f++)
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    float v = acc[b][f][h] * (1.0f / (float)(1 << (2 * f)));
-                    if (!I8) v += __shfl_xor_sync(0xffffffffu, v, 1);   // lanes t, t^1: the digit halves of one vector
-                    const int row = 16 * f + gq + 8 * h;
-                    if (I8) {
-                        if (t == 0) pu[row] = v;
-                    } else if ((t & 1) == 0 && (t >> 1) < NV) {
-                        pu[row * NVT + b * NV + (t >> 1)] = v;
-                    }
-                    acc[b][f][h] = 0.f;
+            for (int h = 0; h < 2; h++) {
+                float v = acc[b][h];
+                if (!I8) v += __shfl_xor_sync(0xffffffffu, v, 1);   // lanes t, t^1: the digit halves of one vector
+                const int row = gq + 8 * h;
+                if (I8) {
+                    if (t == 0) pu[row] = v;
+                } else if ((t & 1) == 0 && (t >> 1) < NV) {
+                    pu[row * NVT + b * NV + (t >> 1)] = v;
                 }
-        dirty = false;
+                acc[b][h] = 0.f;
+            }
     };
 
-    int slot = warp;
-    uint32_t use = 0;                        // how often this slot has been filled before: sequence number / R
-    for (int j = 0; j < nw; j++) {
-        // the slot's barrier must have reached the phase of this use before its parity means
-        // anything: the warp that emptied the slot publishes the use number when it refills it
-        if (use > 0) {
-            ok = false;
-#pragma unroll 1
-            for (int i = 0; i < (1 << 22); i++)
-                if (gen[slot] >= use) {
-                    ok = true;
-                    break;
-                }
-            if (!ok) break;
-        }
-        ok = mbar_wait(bar + slot * 8, use & 1u);
-        if (!ok) break;
-        const uint8_t* tile = ring_p + (size_t)slot * kStBytes;
-        const int gx = (!I8 && a.x_local) ? gx_local : g;
-        const uint4* codes = reinterpret_cast<const uint4*>(tile) + lane;
-        const uint4 s8 = *reinterpret_cast<const uint4*>(tile + kStCodeBytes + gq * 16);
+    // One tile at shared address tp, activations of staged group gx: two MMA chains (steps 0,1
+    // carry the factor 4; steps 2,3 carry 64), joined in integers, the code offset removed,
+    // scale and block exponent applied.
+    auto tile = [&](uint32_t tp, int gx) {
+        const uint4 wd = lds128(tp + (uint32_t)lane * 16u);
+        const float2 sc = __half22float2(u32_as_half2(lds32(tp + sc_off)));
 #pragma unroll
         for (int b = 0; b < NB; b++) {
-            int d[4][4];
-            uint4 xb;
-#pragma unroll
-            for (int m = 0; m < 4; m++) {
-                const uint4 wd = codes[m * 32];
-                if ((m & 1) == 0) xb = xb_lane[((gx * 2 + (m >> 1)) * NB + b) * kXbStride];
-                const uint32_t b0 = (m & 1) ? xb.z : xb.x, b1 = (m & 1) ? xb.w : xb.y;
-#pragma unroll
-                for (int f = 0; f < 4; f++) {
-                    const uint32_t msk = 0x03030303u << (2 * f);
-                    // words (h, j2) = (0,0) (0,1) (1,0) (1,1) are registers a0, a2, a1, a3
-                    if (m == 0) imma<true>(d[f], wd.x & msk, wd.z & msk, wd.y & msk, wd.w & msk, b0, b1);
-                    else imma<false>(d[f], wd.x & msk, wd.z & msk, wd.y & msk, wd.w & msk, b0, b1);
-                }
-            }
-            // group epilogue: remove the code offset, apply scale and block exponent
+            const uint32_t xa = xb_addr + (uint32_t)gx * kXgBytes + (uint32_t)b * (kXbStride * 16u);
+            const uint4 xb0 = lds128(xa);
+            const uint4 xb1 = lds128(xa + NB * kXbStride * 16u);
+            int lo[4], hi[4];
+            // words (h, j2) = (0,0) (0,1) (1,0) (1,1) are registers a0, a2, a1, a3
+            imma<true>(lo, wd.x & 0x03030303u, wd.z & 0x03030303u, wd.y & 0x03030303u, wd.w & 0x03030303u, xb0.x, xb0.y);
+            imma<true>(hi, wd.x & 0x30303030u, wd.z & 0x30303030u, wd.y & 0x30303030u, wd.w & 0x30303030u, xb1.x, xb1.y);
+            imma<false>(lo, wd.x & 0x0c0c0c0cu, wd.z & 0x0c0c0c0cu, wd.y & 0x0c0c0c0cu, wd.w & 0x0c0c0c0cu, xb0.z, xb0.w);
+            imma<false>(hi, wd.x & 0xc0c0c0c0u, wd.z & 0xc0c0c0c0u, wd.y & 0xc0c0c0c0u, wd.w & 0xc0c0c0c0u, xb1.z, xb1.w);
             float fx;
             int soff;
             if (I8) {
                 fx = 1.0f;
-                soff = sx[gx];
+                soff = (int)lds32(xc_addr + (uint32_t)gx * 4u);
             } else {
                 const int v = min(b * NV + (t >> 1), NVT - 1);
-                const uint2 c = reinterpret_cast<const uint2*>(xcst + gx * NVT + v)[t & 1];
+                const uint2 c = lds64(xc_addr + (uint32_t)(gx * NVT + v) * 16u);
                 fx = __uint_as_float(c.x);
                 soff = (int)c.y;
             }
-            const uint32_t sw[4] = {s8.x, s8.y, s8.z, s8.w};
+            // lo = 4 * (steps 0,1), hi = 64 * (steps 2,3): lo * 16 + hi = 64 * (sum of the group) per column
+            const int p0 = (lo[1] * 16 + hi[1]) * kMulA + (lo[0] * 16 + hi[0]) - soff;
+            const int p1 = (lo[3] * 16 + hi[3]) * kMulA + (lo[2] * 16 + hi[2]) - soff;
+            acc[b][0] = fmaf((float)p0, sc.x * fx, acc[b][0]);
+            acc[b][1] = fmaf((float)p1, sc.y * fx, acc[b][1]);
+        }
+    };
+
+    int rem = nw;                            // tiles still to walk
+    int req = nw - min(nw, depth * kSlotTiles);      // tiles still to request (after the first fill)
+    uint32_t koff = 0, kbar = 0;             // the ring slot that holds the next chunk: byte offset, barrier offset
+    const uint32_t kend = (uint32_t)depth * kSlotBytes;
+    uint32_t ph = 0;                         // parity of that slot's current use
+    while (rem > 0) {
+        ok = mbar_wait(bar_w + kbar, ph);
+        if (!ok) break;
+        const uint32_t chunk = ring_w - (uint32_t)lane * 16u + koff;
+        if (rem >= kSlotTiles && g + kSlotTiles <= G) {
+            // common case: a whole chunk inside one row block, straight-line code
 #pragma unroll
-            for (int f = 0; f < 4; f++) {
-                const float2 sc = __half22float2(*reinterpret_cast<const half2*>(&sw[f]));
-                const int o = soff * (1 << (2 * f));
-                const int p0 = I8 ? (d[f][0] - o) : (d[f][1] * mulA + d[f][0] - o);
-                const int p1 = I8 ? (d[f][2] - o) : (d[f][3] * mulA + d[f][2] - o);
-                acc[b][f][0] = fmaf((float)p0, sc.x * fx, acc[b][f][0]);
-                acc[b][f][1] = fmaf((float)p1, sc.y * fx, acc[b][f][1]);
+            for (int q = 0; q < kSlotTiles; q++) tile(chunk + q * kTileBytes, gxi + q);
+            g += kSlotTiles;
+            gxi += kSlotTiles;
+            if (g == G) {
+                flush();
+                g = 0;
+                if (!xloc) gxi = 0;
+                rbr++;
+            }
+        } else {
+            // ragged chunk (end of the warp's range or a row-block boundary inside it)
+            const int nt = min(kSlotTiles, rem);
+            for (int q = 0; q < nt; q++) {
+                tile(chunk + q * kTileBytes, gxi);
+                gxi++;
+                if (++g == G) {              // row block finished (for this warp)
+                    flush();
+                    g = 0;
+                    if (!xloc) gxi = 0;
+                    rbr++;
+                }
             }
         }
-        dirty = true;
-        // refill this slot with sequence number u + R (it belongs to warp (u + R) mod 16)
+        rem -= kSlotTiles;
+        if (kL2Ahead > 0 && a.l2_prefetch) {
+            const int cnext = (nw - req + kSlotTiles - 1) / kSlotTiles + kL2Ahead;
+            if (cnext < nchunks) l2_chunk(cnext);
+        }
+        // every lane is done with the slot: refill it with this warp's next chunk not yet requested
         __syncwarp();
-        {
-            const int u2 = j * kWarps + warp + R;
-            const int w2 = u2 & (kWarps - 1), j2 = u2 >> kWarpsLog2;
-            const int s2 = warp_start(w2, n);
-            if (j2 < warp_start(w2 + 1, n) - s2) {
-                if (lane == 0) gen[slot] = use + 1u;
-                fill_slot(ring + slot * kStBytes, a.packed + (size_t)(t0 + s2 + j2) * kStBytes, bar + slot * 8, lane);
-            }
+        if (req > 0) {
+            fill_slot(ring_w + koff, src_next, bar_w + kbar, lane, min(kSlotTiles, req) * (kTileBytes / 16));
+            src_next += kSlotBytes;
+            req -= kSlotTiles;
         }
-        slot += kWarps;
-        if (slot >= R) {
-            slot -= R;
-            use++;
-        }
-        gx_local++;
-        if (++g == G) {                      // row block finished (for this warp)
-            flush();
-            g = 0;
-            rb++;
-            seg++;
+        koff += kSlotBytes;
+        kbar += 8u;
+        if (koff == kend) {
+            koff = 0;
+            kbar = 0;
+            ph ^= 1u;
         }
     }
-    if (dirty) flush();
+    if (nw > 0 && g != 0) flush();           // tiles walked since the last flush (a flush resets g)
     if (!ok && lane == 0) atomicExch(a.err, TLLM_ERR_TIMEOUT);
     TL(4);
     __syncthreads();
     TL(5);
 
     // ---- reduction: warps of this CTA, then CTAs, row block by row block -----------
-    const int nb = I8 ? 1 : a.batch;
-    const float oscale = FUSEDX ? fused_scale : (I8 ? (a.in_scale_dev ? __ldg(a.in_scale_dev) : a.in_scale) : 1.0f);
-    constexpr int kRec = kStRows * NVT;      // floats of one row block's sums
+    const GemvArgs& e = *reinterpret_cast<const GemvArgs*>(sargs);     // complete since the barrier after staging
+    const int nb = I8 ? 1 : e.batch;
+    // INT8 modes: the 1/64 of the combined MMA results rides on the activation scale
+    const float oscale = FUSEDX ? fused_scale * 0.015625f
+                                : (I8 ? (e.in_scale_dev ? __ldg(e.in_scale_dev) : e.in_scale) * 0.015625f : 1.0f);
+    constexpr int kRec = kTileRows * NVT;    // floats of one row block's sums
 
-    if (kAr && a.ar_world > 0) {
+    if (kAr && e.ar_world > 0) {
         // ---- fused all-reduce: my partial sums go straight into every rank's receive
         // buffer over NVLink as 8-byte {value, launch number} words -- the store of a word
         // is atomic, so the launch number doubles as the arrival flag and no fence or
@@ -767,21 +875,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         if (tracing) ts[2] = globaltimer();
         const unsigned epoch = ar_epoch_prev + 1u;
         const unsigned epar = epoch & 1u;
-        const size_t wslot = (size_t)(epar * a.ar_world + a.ar_rank) * a.ar_rows_max;
+        const size_t wslot = (size_t)(epar * e.ar_world + e.ar_rank) * e.ar_rows_max;
         for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
-            const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);
-            const int wa = warp_of(ta - t0, n), wb = warp_of(tb - 1 - t0, n);
-            for (int idx = lane; idx < kStRows; idx += 32) {
+            for (int idx = lane; idx < kTileRows; idx += 32) {
                 float s = 0.f;
-                for (int w = wa; w <= wb; w++)
-                    if (warp_start(w + 1, n) > warp_start(w, n)) s += part[(size_t)((r_b - rb_first) + w) * kRec + idx];
-                const int r = r_b * kStRows + idx;
-                if (r < a.rows) {
+                for (uint32_t mk = contrib[r_b - rb_first]; mk; mk &= mk - 1u)          // ascending warp order
+                    s += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + idx];
+                const int r = r_b * kTileRows + idx;
+                if (r < e.rows) {
                     const uint2 word = make_uint2(__float_as_uint(s), epoch);
 #pragma unroll
                     for (int dst_rank = 0; dst_rank < kMaxPeers; dst_rank++) {
-                        if (dst_rank < a.ar_world) {
-                            uint2* dst = a.ar_recv[dst_rank] + wslot + r;
+                        if (dst_rank < e.ar_world) {
+                            uint2* dst = e.ar_recv[dst_rank] + wslot + r;
                             asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(word.x), "r"(word.y) : "memory");
                         }
                     }
@@ -790,9 +896,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         }
         __syncthreads();                     // ar_abort initialised; all stores issued
         if (tracing) ts[3] = globaltimer();
-        const int r_lo = rb_first * kStRows, r_hi = min(a.rows, (rb_last + 1) * kStRows);
-        const uint2* recv = a.ar_recv[a.ar_rank] + (size_t)epar * a.ar_world * a.ar_rows_max;
-        const unsigned all = (1u << a.ar_world) - 1u;
+        const int r_lo = rb_first * kTileRows, r_hi = min(e.rows, (rb_last + 1) * kTileRows);
+        const uint2* recv = e.ar_recv[e.ar_rank] + (size_t)epar * e.ar_world * e.ar_rows_max;
+        const unsigned all = (1u << e.ar_world) - 1u;
         bool ok_ar = true;
         for (int r = r_lo + tid; r < r_hi; r += kThreads) {
             // one look at ALL ranks' words per round (independent loads in flight together), then
@@ -807,7 +913,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
                 for (int d = 0; d < kMaxPeers; d++) {
                     tag[d] = 0;
                     if ((pending >> d) & 1u) {
-                        const uint2* src = recv + (size_t)d * a.ar_rows_max + r;
+                        const uint2* src = recv + (size_t)d * e.ar_rows_max + r;
                         asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val[d]), "=r"(tag[d]) : "l"(src) : "memory");
                     }
                 }
@@ -826,15 +932,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
             float v = 0.f;
 #pragma unroll
             for (int d = 0; d < kMaxPeers; d++)
-                if (d < a.ar_world) v += __uint_as_float(val[d]);      // rank order: the same sum on every rank
-            a.y[r] = __float2half_rn(v);
+                if (d < e.ar_world) v += __uint_as_float(val[d]);      // rank order: the same sum on every rank
+            e.y[r] = __float2half_rn(v);
         }
-        if (!ok_ar) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+        if (!ok_ar) atomicExch(e.err, TLLM_ERR_TIMEOUT);
         __syncthreads();
-        if (tid == 0) a.ar_epoch[blockIdx.x] = epoch;
+        if (tid == 0) e.ar_epoch[blockIdx.x] = epoch;
         if (tracing) {
             ts[4] = globaltimer();
-            unsigned long long* rec = a.ar_trace + (size_t)(epoch % (unsigned)a.ar_trace_cap) * 8;
+            unsigned long long* rec = e.ar_trace + (size_t)(epoch % (unsigned)e.ar_trace_cap) * 8;
 #pragma unroll
             for (int i = 0; i < 5; i++) rec[i] = ts[i];
             rec[5] = epoch;
@@ -842,36 +948,39 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
         return;
     }
 
-    uint2* myrec = a.ws + (size_t)blockIdx.x * a.ws_stride;
-    const int rec1 = a.ws_stride >> 1;        // offset of a CTA's second record
-    constexpr int kW = kRec / 32;             // words per lane in one record
-    constexpr int kChunk = (kW >= 8) ? 1 : ((kW >= 4) ? 2 : 4);      // records polled together
+    uint2* myrec = e.ws + (size_t)blockIdx.x * e.ws_stride;
+    const int rec1 = e.ws_stride >> 1;        // offset of a CTA's second record
+    constexpr int kW = (kRec + 31) / 32;      // words per lane in one record (kRec = 16, 32 or 64)
+    constexpr int kChunk = 4 / kW;            // records polled together
+    const bool mine = (kRec >= 32) || lane < kRec;      // this lane holds a word of the record
     bool ok_c = true;
     for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
-        const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);     // this CTA's super-tiles of the block
-        const int wa = warp_of(ta - t0, n), wb = warp_of(tb - 1 - t0, n);
+        const int ta = max(t0, r_b * G), tb = min(t0 + n, (r_b + 1) * G);     // this CTA's tiles of the block
         const bool full = (tb - ta == G);
+        const uint32_t mk0 = contrib[r_b - rb_first];
         float s[kW];
 #pragma unroll
         for (int i = 0; i < kW; i++) {
             const int idx = lane + 32 * i;
             float v = 0.f;
-            for (int w = wa; w <= wb; w++)
-                if (warp_start(w + 1, n) > warp_start(w, n))       // warps without super-tiles wrote nothing
-                    v += part[(size_t)((r_b - rb_first) + w) * kRec + idx];
+            if (mine)
+                for (uint32_t mk = mk0; mk; mk &= mk - 1u)                     // ascending warp order
+                    v += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + idx];
             s[i] = v;
         }
         if (!full) {
             // This row block is shared with neighbouring CTAs (K is split across them).  All but
             // the last of them publish their sums and are done; the last gathers.
-            const int c_a = part_of(r_b * G, a.part_q, a.part_r);
-            const int c_b = part_of((r_b + 1) * G - 1, a.part_q, a.part_r);
+            const int c_a = part_of(r_b * G, e.part_q, e.part_r);
+            const int c_b = part_of((r_b + 1) * G - 1, e.part_q, e.part_r);
             if ((int)blockIdx.x != c_b) {
                 uint2* rec = myrec + ((r_b == rb_first) ? 0 : rec1);
+                if (mine) {
 #pragma unroll
-                for (int i = 0; i < kW; i++)
-                    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};"
-                                 ::"l"(rec + lane + 32 * i), "r"(__float_as_uint(s[i])), "r"(1u) : "memory");
+                    for (int i = 0; i < kW; i++)
+                        asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};"
+                                     ::"l"(rec + lane + 32 * i), "r"(__float_as_uint(s[i])), "r"(1u) : "memory");
+                }
                 continue;
             }
             float tot[kW];
@@ -885,9 +994,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
                 for (int cc = 0; cc < kChunk; cc++) {
                     const int c = min(c0 + cc, c_b - 1);
                     // record 0 of a CTA belongs to its first row block, record 1 to its last
-                    const int c_rb = (int)((unsigned)part_start(c, a.part_q, a.part_r) / (unsigned)G);
-                    rec[cc] = a.ws + (size_t)c * a.ws_stride + ((r_b == c_rb) ? 0 : rec1) + lane;
-                    if (c0 + cc < c_b) pending |= ((1u << kW) - 1u) << (cc * kW);
+                    const int c_rb = (int)((unsigned)part_start(c, e.part_q, e.part_r) / (unsigned)G);
+                    rec[cc] = e.ws + (size_t)c * e.ws_stride + ((r_b == c_rb) ? 0 : rec1) + lane;
+                    if (c0 + cc < c_b && mine) pending |= ((1u << kW) - 1u) << (cc * kW);
+#pragma unroll
+                    for (int i = 0; i < kW; i++) val[cc][i] = 0u;
                 }
                 // all words of the chunk are requested together, then only the missing ones; a
                 // wait that expires (about half a second) ends every later wait of this CTA at once
@@ -919,7 +1030,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
                 if (pending) ok_c = false;
 #pragma unroll
                 for (int cc = 0; cc < kChunk; cc++)
-                    if (c0 + cc < c_b) {
+                    if (c0 + cc < c_b && mine) {
 #pragma unroll
                         for (int i = 0; i < kW; i++) {
                             tot[i] += __uint_as_float(val[cc][i]);
@@ -931,43 +1042,45 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const GemvArgs
 #pragma unroll
             for (int i = 0; i < kW; i++) s[i] += tot[i];            // own part last: CTA order
         }
+        if (mine) {
 #pragma unroll
-        for (int i = 0; i < kW; i++) {
-            const int idx = lane + 32 * i;
-            const int r = r_b * kStRows + idx / NVT, b = idx % NVT;
-            if (r < a.rows && b < nb) *out_ptr(a, b, r) = __float2half_rn(s[i] * oscale);
+            for (int i = 0; i < kW; i++) {
+                const int idx = lane + 32 * i;
+                const int r = r_b * kTileRows + idx / NVT, b = idx % NVT;
+                if (r < e.rows && b < nb) *out_ptr(e, b, r) = __float2half_rn(s[i] * oscale);
+            }
         }
     }
-    if (!ok_c) atomicExch(a.err, TLLM_ERR_TIMEOUT);
+    if (!ok_c) atomicExch(e.err, TLLM_ERR_TIMEOUT);
     TL(6);
 }
 
 // ---------------------------------------------------------------------------
 // Repack: reference layout -> packed layout, and back
 // ---------------------------------------------------------------------------
-// one thread per code word of the packed matrix; the threads of words (m = 0, t = 0, j2 = 0)
-// also write their rows' scales.  Counts sign bits that have no nonzero bit.
+// one thread per code word of the packed matrix; the threads of words (t = 0, j2 = 0) also write
+// their row's scale.  Counts sign bits that have no nonzero bit.
 __global__ void repack_kernel(const uint32_t* __restrict__ nz, const uint32_t* __restrict__ sg,
                               const half* __restrict__ scales, uint8_t* __restrict__ packed,
                               int rows, int cols, int* __restrict__ noncanon)
 {
     const int groups = cols / kGroup, wpr = cols / 32;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long nst = (long long)((rows + kStRows - 1) / kStRows) * groups;
-    if (idx >= nst * 512) return;
-    const long long st = idx >> 9;
-    const int wi = (int)(idx & 511);
-    const int m = wi >> 7, lane = (wi >> 2) & 31, i = wi & 3;
+    const long long ntiles = (long long)((rows + kTileRows - 1) / kTileRows) * groups;
+    if (idx >= ntiles * 128) return;
+    const long long tile = idx >> 7;
+    const int wi = (int)(idx & 127);
+    const int lane = wi >> 2, i = wi & 3;
     const int gq = lane >> 2, t = lane & 3, h = i >> 1, j2 = i & 1;
-    const int rb = (int)(st / groups), g = (int)(st % groups);
-    const int bit0 = 16 * j2 + 4 * t;                       // first of this word's four bits in the mask word
+    const int rb = (int)(tile / groups), g = (int)(tile % groups);
+    const int r = rb * kTileRows + gq + 8 * h;
+    const int bit0 = 16 * j2 + 4 * t;                       // first of this word's four bits in each mask word
     uint32_t word = 0, stray = 0;
-    for (int f = 0; f < 4; f++) {
-        const int r = rb * kStRows + 16 * f + gq + 8 * h;
+    for (int f = 0; f < 4; f++) {                           // mask word f of the group: columns 32f .. 32f+31
         uint32_t a = 0, s = 0;
         if (r < rows) {
-            a = nz[(size_t)r * wpr + g * 4 + m];
-            s = sg[(size_t)r * wpr + g * 4 + m];
+            a = nz[(size_t)r * wpr + g * 4 + f];
+            s = sg[(size_t)r * wpr + g * 4 + f];
         }
         a = (a >> bit0) & 0xfu;
         s = (s >> bit0) & 0xfu;
@@ -978,15 +1091,12 @@ __global__ void repack_kernel(const uint32_t* __restrict__ nz, const uint32_t* _
             word |= code << (8 * j + 2 * f);
         }
     }
-    reinterpret_cast<uint32_t*>(packed + (size_t)st * kStBytes)[wi] = word;
+    uint8_t* tp = packed + (size_t)tile * kTileBytes;
+    reinterpret_cast<uint32_t*>(tp)[wi] = word;
     if (stray) atomicAdd(noncanon, (int)stray);
-    if (m == 0 && t == 0 && j2 == 0) {
-        half* sp = reinterpret_cast<half*>(packed + (size_t)st * kStBytes + kStCodeBytes);
-        for (int f = 0; f < 4; f++) {
-            const int r64 = 16 * f + gq + 8 * h, r = rb * kStRows + r64;
-            sp[st_scale_index(r64)] = (r < rows) ? scales[(size_t)r * groups + g] : __float2half(0.f);
-        }
-    }
+    if (t == 0 && j2 == 0)
+        reinterpret_cast<half*>(tp + kTileCodeBytes)[tile_scale_index(gq + 8 * h)] =
+            (r < rows) ? scales[(size_t)r * groups + g] : __float2half(0.f);
 }
 
 // one thread per (row, mask word): rebuilds canonical nonzero/sign words; the
@@ -998,27 +1108,27 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ packed, uint32_t* __re
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)rows * wpr) return;
     const int r = (int)(idx / wpr), wd = (int)(idx % wpr);
-    const int g = wd / 4, m = wd % 4;          // mask word wd covers group columns 32m .. 32m+31 = k32 step m
-    const uint8_t* tp = packed + ((size_t)(r / kStRows) * groups + g) * kStBytes;
+    const int g = wd / 4, f = wd % 4;          // mask word wd covers group columns 32f .. 32f+31
+    const uint8_t* tp = packed + ((size_t)(r / kTileRows) * groups + g) * kTileBytes;
     const uint32_t* cw = reinterpret_cast<const uint32_t*>(tp);
-    const int r64 = r % kStRows;
+    const int r16 = r % kTileRows;
     uint32_t a = 0, s = 0;
     for (int c = 0; c < 32; c++) {
         int word, shift;
-        st_locate(r64, 32 * m + c, word, shift);
+        tile_locate(r16, 32 * f + c, word, shift);
         const uint32_t code = (cw[word] >> shift) & 3u;
         if (code != 1u) a |= 1u << c;
         if (code == 2u) s |= 1u << c;
     }
     nz[idx] = a;
     sg[idx] = s;
-    if (m == 0) scales[(size_t)r * groups + g] = reinterpret_cast<const half*>(tp + kStCodeBytes)[st_scale_index(r64)];
+    if (f == 0) scales[(size_t)r * groups + g] = reinterpret_cast<const half*>(tp + kTileCodeBytes)[tile_scale_index(r16)];
 }
 
 // ---------------------------------------------------------------------------
 // Host side: scratch, registry, launch
 // ---------------------------------------------------------------------------
-constexpr int kMaxRowBlocks = 1 << 16;          // rows up to 4,194,304
+constexpr int kMaxRowBlocks = 1 << 18;          // rows up to 4,194,304
 struct DeviceScratch {
     uint2* ws = nullptr;       // [kTickets][kMaxCtas][2][kRecFloats] {value, flag}, all zero between launches
     int* misc = nullptr;       // [0] non-canonical bit counter of the last prepare, [1] device error flag
@@ -1065,10 +1175,10 @@ const uint8_t* lookup_packed(const void* nz, int rows, int cols)
 
 size_t packed_bytes(int rows, int cols)
 {
-    return (size_t)((rows + kStRows - 1) / kStRows) * (size_t)(cols / kGroup) * kStBytes;
+    return (size_t)((rows + kTileRows - 1) / kTileRows) * (size_t)(cols / kGroup) * kTileBytes;
 }
 
-int packed_row_align() { return kStRows; }
+int packed_row_align() { return kTileRows; }
 
 // Partition of the matrix over CTAs and the shared-memory layout of one launch; the same for
 // every entry point (regular, no-allocation, fused all-reduce), which differ only in where the
@@ -1080,10 +1190,10 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
 {
     const int rows = a.rows, cols = a.cols;
     a.groups = cols / kGroup;
-    const int nrb = (rows + kStRows - 1) / kStRows;
-    if (nrb > kMaxRowBlocks) return fail(TLLM_ERR_SHAPE, "rows=%d exceeds %d", rows, kMaxRowBlocks * kStRows);
-    if ((long long)nrb * a.groups >= (1ll << 26))
-        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: more than 2^26 super-tiles", rows, cols);
+    const int nrb = (rows + kTileRows - 1) / kTileRows;
+    if (nrb > kMaxRowBlocks) return fail(TLLM_ERR_SHAPE, "rows=%d exceeds %d", rows, kMaxRowBlocks * kTileRows);
+    if ((long long)nrb * a.groups >= (1ll << 27))
+        return fail(TLLM_ERR_SHAPE, "rows=%d cols=%d: more than 2^27 tiles", rows, cols);
     const int tiles = nrb * a.groups;
     const int grid_max = sms < max_ctas ? sms : max_ctas;
     const bool fusedx = (mode == kI8Norm || mode == kI8Silu || mode == kI8Quant);
@@ -1091,7 +1201,7 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     const int per_cta_rb = (nrb + grid_max - 1) / grid_max;
 
     // Shared-memory layout for one way of cutting the matrix: activations | group constants |
-    // partial sums | (fused staging) | mbarriers | use numbers | ring.  Returns the bytes in
+    // partial sums | contributor masks | (fused staging) | mbarriers | ring.  Returns the bytes in
     // front of the ring.
     auto layout = [&](int aligned, int* grid, int* n_max_out) {
         a.aligned = aligned;
@@ -1099,18 +1209,20 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
         *grid = items < grid_max ? items : grid_max;
         a.part_q = items / *grid;
         a.part_r = items % *grid;
-        const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * (aligned ? a.groups : 1);    // super-tiles of the largest CTA
+        const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * (aligned ? a.groups : 1);    // tiles of the largest CTA
         *n_max_out = n_max;
         a.x_local = (!i8 && n_max < a.groups) ? 1 : 0;
         const int gstaged = a.x_local ? n_max : a.groups;
-        size_t off = i8 ? (size_t)cols : (size_t)gstaged * nvt * 384;
+        size_t off = i8 ? (size_t)cols * 2 : (size_t)gstaged * nvt * 512;
         off = (off + 15) & ~(size_t)15;
         a.off_xcst = (int)off;
         off += i8 ? (size_t)a.groups * sizeof(int) : (size_t)gstaged * nvt * 16;
         off = (off + 15) & ~(size_t)15;
         a.off_part = (int)off;
         const int max_rb_per_cta = aligned ? (a.part_q + 1) : ((a.part_q + 1 + a.groups - 1) / a.groups + 1);
-        off += (size_t)(max_rb_per_cta + kWarps) * kStRows * nvt * sizeof(float);
+        off += (size_t)(max_rb_per_cta + kWarps) * kTileRows * nvt * sizeof(float);
+        a.off_mask = (int)off;
+        off += (size_t)(max_rb_per_cta + 1) * sizeof(uint32_t);
         if (fusedx) {
             off = (off + 15) & ~(size_t)15;
             a.off_xtmp = (int)off;
@@ -1119,8 +1231,6 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
         off = (off + 15) & ~(size_t)15;
         a.off_bar = (int)off;
         off += (size_t)kMaxSlots * 8;
-        a.off_gen = (int)off;
-        off += (size_t)kMaxSlots * 4;
         off = (off + 127) & ~(size_t)127;
         a.off_ring = (int)off;
         return off;
@@ -1132,26 +1242,29 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     // that leaves: such a launch has all its weights on the chip before the kernel in front of
     // it ends, so its time after that is a few hundred nanoseconds of arithmetic either way,
     // while a combine across CTAs costs a store, a load and a poll on top.  Otherwise the
-    // matrix is cut at super-tile granularity (K is split across CTAs).
+    // matrix is cut at tile granularity (K is split across CTAs).
+    // Chunks (ring slots) a CTA of n tiles walks: every warp rounds its share up to whole chunks.
+    auto chunks_of = [](int n) { return kWarps * (((n + kWarps - 1) / kWarps + kSlotTiles - 1) / kSlotTiles); };
     int grid = 0, n_max = 0;
     size_t off = layout(1, &grid, &n_max);
     bool aligned = force_aligned || (nrb >= grid_max && (double)nrb / ((double)per_cta_rb * grid_max) >= 0.8);
-    if (!aligned && off + (size_t)n_max * kStBytes <= kCoResidentBytes && n_max <= kMaxSlots) aligned = true;
+    if (!aligned && chunks_of(n_max) <= kMaxSlots && off + (size_t)chunks_of(n_max) * kSlotBytes <= kCoResidentBytes)
+        aligned = true;
     if (!aligned) off = layout(0, &grid, &n_max);
     a.late_release = release_rule(rows, cols);
     // Ring: what a CTA can use, bounded by what lets two CTAs share the SM (the launch that
     // follows prefetches its weights beside this one); a problem whose activations leave less
-    // than 24 slots that way runs one CTA per SM with all of the shared memory.
-    const int want = n_max < kWarps ? kWarps : (n_max > kMaxSlots ? kMaxSlots : n_max);
-    long long slots = ((long long)kCoResidentBytes - (long long)off) / kStBytes;
-    if (slots < want && slots < 24) slots = ((long long)kMaxSmemBytes - (long long)off) / kStBytes;
+    // than 96 tiles of ring that way runs one CTA per SM with all of the shared memory.
+    const int want = chunks_of(n_max) > kMaxSlots ? kMaxSlots : chunks_of(n_max);
+    long long slots = ((long long)kCoResidentBytes - (long long)off) / kSlotBytes;
+    if (slots < kWarps || (slots < want && slots * kSlotTiles < 96)) slots = ((long long)kMaxSmemBytes - (long long)off) / kSlotBytes;
     if (slots > want) slots = want;
     if (slots < kWarps)
         return fail(TLLM_ERR_SIZE, "rows=%d cols=%d with %d vectors per pass needs more shared memory than an SM has "
                     "(%zu bytes before the ring)", rows, cols, nvt, off);
     a.ring_slots = (int)slots;
-    a.l2_prefetch = (n_max > (int)slots) ? 1 : 0;
-    off += (size_t)slots * kStBytes;
+    a.l2_prefetch = (chunks_of(n_max) > (int)slots) ? 1 : 0;
+    off += (size_t)slots * kSlotBytes;
     *grid_out = grid;
     *smem_out = off;
     return TLLM_OK;
@@ -1278,8 +1391,8 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
 }
 
 // Several matrices that share x and the column count (q/k/v; gate/up): matrices that were
-// packed back to back (every row count but the last a multiple of 64) are one contiguous
-// super-tile array and are streamed as ONE matrix in one launch, outputs scattered per
+// packed back to back (every row count but the last a multiple of 16) are one contiguous
+// tile array and are streamed as ONE matrix in one launch, outputs scattered per
 // segment; otherwise one launch each.
 // x is FP16 (xq == nullptr) or INT8 with its scale in device memory.
 static int gemv_packed_multi_any(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
@@ -1293,7 +1406,7 @@ static int gemv_packed_multi_any(int count, const uint8_t* const* packed, half* 
         int total = 0;
         for (int i = 0; i < count; i++) {
             if (i + 1 < count)
-                contiguous = contiguous && (rows[i] % kStRows == 0) && (packed[i + 1] == packed[i] + packed_bytes(rows[i], cols));
+                contiguous = contiguous && (rows[i] % kTileRows == 0) && (packed[i + 1] == packed[i] + packed_bytes(rows[i], cols));
             seg.rows[i] = rows[i];
             seg.y[i] = y[i];
             total += rows[i];
@@ -1376,12 +1489,12 @@ int launch_gemv_packed(const uint8_t* packed, const half* x, half* y, int batch,
 // the allocator is forbidden (a real-time loop, a stream capture), or a process whose
 // memory budget is audited up front.  For them the split-K combine scratch of the
 // GEMV lives in this fixed array instead of a lazily allocated buffer.  Every GPU that
-// loads the library carries these 160 KB until the process exits.
-//   [0, 163840)       partial-sum records, kNoAllocMaxCtas x 2 x 64 words {value, flag} (one vector)
-//   [163840, 163844)  device error flag
+// loads the library carries these 40 KB until the process exits.
+//   [0, 40960)        partial-sum records, kNoAllocMaxCtas x 2 x 16 words {value, flag} (one vector)
+//   [40960, 40964)    device error flag
 constexpr int kNoAllocMaxRows = 65536;
 constexpr int kNoAllocMaxCtas = 160;
-constexpr size_t kNoAllocWsBytes = (size_t)kNoAllocMaxCtas * 2 * kStRows * sizeof(uint2);
+constexpr size_t kNoAllocWsBytes = (size_t)kNoAllocMaxCtas * 2 * kTileRows * sizeof(uint2);
 constexpr size_t kNoAllocBytes = kNoAllocWsBytes + 256;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
@@ -1422,7 +1535,7 @@ static int noalloc_device(NoAllocDevice** out)
 // call outside any stream capture.  All calls share the one scratch array, which
 // keeps what the previous call left: the records (their flags must start at zero) are
 // cleared on `stream` before each launch, and two calls whose kernels overlap on the GPU
-// (different streams) race.  With one vector a partial record is 64 words, so the records
+// (different streams) race.  With one vector a partial record is 16 words, so the records
 // are laid out at that stride here (ws_stride), and the grid is capped at kNoAllocMaxCtas.
 int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, int rows, int cols,
                                cudaStream_t stream)
@@ -1445,9 +1558,9 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     if ((st = plan_gemv(a, nd->sms, kF16, 1, kNoAllocMaxCtas, false, &grid, &smem))) return st;
     a.ws = reinterpret_cast<uint2*>(nd->base);
     a.err = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
-    a.ws_stride = 2 * kStRows;
+    a.ws_stride = 2 * kTileRows;
     // the records' flags must start at zero; a call that was cut short may have left some set
-    if (cudaMemsetAsync(a.ws, 0, (size_t)grid * 2 * kStRows * sizeof(uint2), stream) != cudaSuccess) {
+    if (cudaMemsetAsync(a.ws, 0, (size_t)grid * 2 * kTileRows * sizeof(uint2), stream) != cudaSuccess) {
         cudaGetLastError();
         return fail(TLLM_ERR_LAUNCH, "clearing the scratch records failed");
     }
@@ -1544,7 +1657,7 @@ int weight_prepare(const uint32_t* nz, const uint32_t* sg, const half* scales, i
     int st = get_scratch(&s);
     if (st) return st;
     cudaMemsetAsync(s->misc, 0, sizeof(int), stream);
-    const long long threads = (long long)((rows + kStRows - 1) / kStRows) * (cols / kGroup) * 512;
+    const long long threads = (long long)((rows + kTileRows - 1) / kTileRows) * (cols / kGroup) * 128;
     repack_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(nz, sg, scales, packed, rows, cols, s->misc);
     if ((st = check_launch("repack"))) return st;
     int stray = 0;

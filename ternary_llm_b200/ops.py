@@ -175,7 +175,7 @@ def prepare_group(weights, register: bool = False, keep_source: bool = False):
     """Packs several matrices that share their input vector (q, k, v; gate, up) back to back
     in one allocation.  weights: list of (nonzero_masks, sign_masks, scales, rows, cols).
     ternary_gemv_packed_multi on the returned list streams them as ONE matrix in a single
-    launch (every row count but the last must be a multiple of 64 for that)."""
+    launch (every row count but the last must be a multiple of 16 for that)."""
     sizes = [packed_bytes(r, c) for (_, _, _, r, c) in weights]
     buf = torch.empty(sum(sizes), dtype=torch.uint8, device=weights[0][0].device)
     out, off = [], 0

@@ -33,7 +33,7 @@ def _prep(nz, sg, sc, register=False):
 def test_repack_round_trip_bit_exact(n, k):
     nz, sg, sc, _ = oracle.make_case(n, k, seed=n + k)
     w = _prep(nz, sg, sc)
-    assert w.packed.numel() == ((n + 63) // 64) * (k // 128) * 2176
+    assert w.packed.numel() == ((n + 15) // 16) * (k // 128) * 544
     nz2, sg2, sc2 = w.unpack()
     torch.cuda.synchronize()
     assert (nz2.cpu().numpy().view(np.uint32) == nz).all()
@@ -287,7 +287,7 @@ def test_group_packed_back_to_back_runs_as_one_matrix():
     """prepare_group + the fused entry points: same results as one call per matrix, FP16 and INT8."""
     from ternary_llm_b200 import layer_ops, synth
     k = 2048
-    shapes = (1024, 256, 272)          # the last row count need not be a multiple of 64
+    shapes = (1024, 256, 272)          # the last row count need not be a multiple of 16
     mats = []
     for i, n in enumerate(shapes):
         nz, sg, sc = synth.random_ternary_weight(n, k, seed=70 + i, device="cuda")

@@ -4,7 +4,7 @@ tokens, and the per-rank shapes of the LLaMA-70B tensor-parallel split on one GP
 
 Weights are drawn on the device (seeded); the oracle (float64, the 2e-3 * sum|scale*t*x|
 bound plus half an FP16 ulp) is evaluated on a sample of output rows that always holds the
-first and the last 64-row block and the rows either side of every 1/37 of the matrix, which
+first and the last 64 rows and the rows either side of every 1/37 of the matrix, which
 is where a row block changes hands between CTAs.  Every output, sampled or not, must be
 finite and -- a size-independent property -- doubling the activations must double every
 output exactly.

@@ -36,7 +36,7 @@ def _dev(a):
 
 
 # (1024, 4096) splits K across SMs, so the scratch records and counters are exercised;
-# so does (4096, 4096) with longer ranges per SM; (40, 384) has ragged rows and one CTA.
+# (4096, 4096) takes whole row blocks per CTA; (40, 384) has ragged rows.
 @pytest.mark.parametrize("n,k", [(1024, 4096), (4096, 4096), (40, 384)])
 def test_noalloc_matches_regular_entry_point_twice(n, k):
     torch.cuda.set_device(0)
