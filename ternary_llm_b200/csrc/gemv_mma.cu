@@ -81,6 +81,12 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 #define TLLM_GEMV_CORESIDENT_BYTES (112 * 1024)
 #endif
 constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
+// A ring that two co-resident CTAs allow but that holds fewer slots than this (and less than the
+// CTA's whole share) is given up for one CTA per SM with all of the shared memory.
+#ifndef TLLM_GEMV_MIN_SHARED_SLOTS
+#define TLLM_GEMV_MIN_SHARED_SLOTS 24
+#endif
+constexpr int kMinSharedSlots = TLLM_GEMV_MIN_SHARED_SLOTS;
 constexpr size_t kMaxSmemBytes = 226 * 1024;      // dynamic part; the kernel also has a few static bytes
 // How far beyond the ring a warp asks for its weights to be brought into L2, in chunks (0 = off).
 // The ring is bounded by shared memory: 63 KB in flight per SM at the 2 us an HBM access takes
@@ -626,6 +632,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     if (tracing) ts[0] = globaltimer();
     TL_BEGIN();
     TL(0);
+#ifdef TLLM_TIMELINE
+    if (threadIdx.x == 0)
+        g_tl[tl_slot][blockIdx.x][7] = (unsigned long long)a.aligned | ((unsigned long long)a.ring_slots << 8) |
+                                       ((unsigned long long)gridDim.x << 20) | ((unsigned long long)a.part_q << 32);
+#endif
     // Kernel parameters sit in a constant bank that is new with every launch: the first read of
     // each of its cache lines goes out to memory.  Every line is read once here, where the
     // latency hides behind the previous kernel, and the part of the kernel that runs after the
@@ -1254,10 +1265,10 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     a.late_release = release_rule(rows, cols);
     // Ring: what a CTA can use, bounded by what lets two CTAs share the SM (the launch that
     // follows prefetches its weights beside this one); a problem whose activations leave less
-    // than 96 tiles of ring that way runs one CTA per SM with all of the shared memory.
+    // than kMinSharedSlots slots that way runs one CTA per SM with all of the shared memory.
     const int want = chunks_of(n_max) > kMaxSlots ? kMaxSlots : chunks_of(n_max);
     long long slots = ((long long)kCoResidentBytes - (long long)off) / kSlotBytes;
-    if (slots < kWarps || (slots < want && slots * kSlotTiles < 96)) slots = ((long long)kMaxSmemBytes - (long long)off) / kSlotBytes;
+    if (slots < kWarps || (slots < want && slots < kMinSharedSlots)) slots = ((long long)kMaxSmemBytes - (long long)off) / kSlotBytes;
     if (slots > want) slots = want;
     if (slots < kWarps)
         return fail(TLLM_ERR_SIZE, "rows=%d cols=%d with %d vectors per pass needs more shared memory than an SM has "
