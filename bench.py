@@ -283,88 +283,87 @@ def _log(rank, msg):
 
 
 def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
+    """N > 1: the LLaMA-70B-shape layer stack (norms, q/k/v, RoPE + KV append, attention over a
+    2048-token FP16 cache, o, SwiGLU, down) tensor-parallel over the ranks, one token per step.
+    Headline: batch 1 with the all-reduce fused into the row-parallel GEMV.  Beside it: the same
+    stack at batch 32 (library all-reduce) and the projections alone (the weight stream without
+    attention and element-wise kernels)."""
+    from ternary_llm_b200.tp_stack import StackConfig, TpLayerStack
+    KV_LEN = 2048
     shapes = tp_shapes(world)
     n_layers = args.layers if args.layers > 0 else LAYERS_70B
+    cfg = StackConfig(hidden=H70, n_heads=Q70 // 128, n_kv_heads=KV70 // 128, head_dim=128, intermediate=I70,
+                      max_seq_len=KV_LEN)
+    assert [(n, r, c) for n, r, c in cfg.shard_shapes(world)] == shapes
     full = [("q", Q70, H70), ("k", KV70, H70), ("v", KV70, H70), ("o", H70, Q70), ("gate", I70, H70),
             ("up", I70, H70), ("down", H70, I70)]
-    step_bytes = n_layers * sum(gemv_bytes(n, k) for _, n, k in full)
-    layers = []
-    _log(rank, f"generating {n_layers} layers of tp{world} shards")
-    for li in range(n_layers):
-        src = []
-        for mi, (_, n, k) in enumerate(shapes):
-            nz, sg, sc = synth.random_ternary_weight(n, k, seed=1_000_000 * rank + 100 * li + mi, device=dev)
-            src.append((nz, sg, sc, n, k))
-        # q|k|v and gate|up shards are packed back to back: one launch per group
-        mats = tl.prepare_group(src[0:3])
-        mats.append(tl.PreparedWeight(*src[3], register=False, keep_source=False))
-        mats += tl.prepare_group(src[4:6])
-        mats.append(tl.PreparedWeight(*src[6], register=False, keep_source=False))
-        if li == 0:
-            parity_src = {"o": src[3][:3], "down": src[6][:3]}     # this rank's shards, reference layout
-        del src
-        layers.append(mats)
-    gen = torch.Generator(device=dev).manual_seed(99)
-    x_h = torch.randn(H70, generator=gen, device=dev).half()            # layer input (replicated)
-    x_attn = torch.randn(Q70 // world, generator=gen, device=dev).half()  # local slice of the attention output
-    x_ffn = torch.randn(I70 // world, generator=gen, device=dev).half()   # local slice of the SwiGLU output
-    yq = torch.zeros(Q70 // world, dtype=torch.float16, device=dev)
-    yk = torch.zeros(KV70 // world, dtype=torch.float16, device=dev)
-    yv = torch.zeros(KV70 // world, dtype=torch.float16, device=dev)
-    yo = torch.zeros(H70, dtype=torch.float16, device=dev)
-    yg = torch.zeros(I70 // world, dtype=torch.float16, device=dev)
-    yu = torch.zeros(I70 // world, dtype=torch.float16, device=dev)
-    yd = torch.zeros(H70, dtype=torch.float16, device=dev)
+    weight_bytes = n_layers * sum(gemv_bytes(n, k) for _, n, k in full)
+    kv_bytes = n_layers * 2 * KV70 * KV_LEN * 2                 # K and V of every layer, read once per token
+    step_bytes = weight_bytes + kv_bytes
+    parity_src = {}
+    ones = torch.ones(H70, dtype=torch.float16, device=dev)
 
+    def layer_sources():
+        for li in range(n_layers):
+            src = {"attn_norm": ones, "ffn_norm": ones}
+            for mi, (name, n, k) in enumerate(shapes):
+                src[name] = synth.random_ternary_weight(n, k, seed=1_000_000 * rank + 100 * li + mi, device=dev)
+            if li == 0:
+                parity_src.update({"o": src["o"], "down": src["down"]})     # this rank's shards, reference layout
+            yield src
+
+    _log(rank, f"generating {n_layers} layers of tp{world} shards")
     fused = args.allreduce == "fused"
-    ar = tl.FusedAllReduce(dist.group.WORLD, H70, dev) if fused else None
+    stack = TpLayerStack(cfg, layer_sources(), rank, world, dev, dist.group.WORLD, allreduce=args.allreduce, batch=1)
+    gen = torch.Generator(device=dev).manual_seed(99)
+    stack.k_cache.copy_(torch.randn(stack.k_cache.shape, generator=gen, device=dev, dtype=torch.float16))
+    stack.v_cache.copy_(torch.randn(stack.v_cache.shape, generator=gen, device=dev, dtype=torch.float16))
+    x_h = (torch.randn(1, H70, generator=gen, device=dev) * 0.5).half()   # the token's embedding (replicated)
+    x_attn = torch.randn(Q70 // world, generator=gen, device=dev).half()  # inputs of the projections-only pass
+    x_ffn = torch.randn(I70 // world, generator=gen, device=dev).half()
+    yq, yk, yv, yo, yg, yu, yd = (stack.q[0], stack.k[0], stack.v[0], stack.yo[0], stack.g[0], stack.u[0], stack.yd[0])
 
     def row_parallel(w, x_local, y):
-        if fused:      # partial sums exchanged by the GEMV kernel itself over peer memory
-            tl.ternary_gemv_packed_allreduce(w, x_local, y, ar)
-        else:          # library route: GEMV, then NCCL all-reduce of the FP16 vector
-            tl.ternary_gemv_packed(w, x_local, y)
-            dist.all_reduce(y)
+        stack._row(w, x_local, y)
+
+    def projections_only():
+        for (qkv, o, gu, down, _, _) in stack.layers:
+            tl.ternary_gemv_packed_multi(qkv, x_h[0], [yq, yk, yv])     # column shards, one input
+            row_parallel(o, x_attn, yo)
+            tl.ternary_gemv_packed_multi(gu, x_h[0], [yg, yu])
+            row_parallel(down, x_ffn, yd)
 
     def launch_step():
-        n = 0
-        for mats in layers:
-            q, k, v, o, g, u, d = mats
-            tl.ternary_gemv_packed_multi([q, k, v], x_h, [yq, yk, yv])   # column shards, one input
-            row_parallel(o, x_attn, yo)
-            tl.ternary_gemv_packed_multi([g, u], x_h, [yg, yu])
-            row_parallel(d, x_ffn, yd)
-            n += 7
-        return n
+        stack.step(x_h, KV_LEN - 1)
 
     _log(rank, "weights ready; first eager step")
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
-        launches = launch_step()
+        launch_step()
         torch.cuda.synchronize()
+        tl.check_device_errors()
+        assert bool(torch.isfinite(stack.res).all()), "non-finite residual stream"
         # parity of the exchange, outside every timed region: layer 0's o and down through the
         # same row-parallel path, rank 0 compares sampled rows with the CPU oracle on the
         # gathered shards (sum over ranks of W_r x_r)
         parity = tp_parity(torch, dist, rank, world, dev, parity_src,
-                           {"o": (layers[0][3], x_attn, yo), "down": (layers[0][6], x_ffn, yd)}, row_parallel)
-        del parity_src
+                           {"o": (stack.layers[0][1], x_attn, yo), "down": (stack.layers[0][3], x_ffn, yd)}, row_parallel)
+        parity_src.clear()
         _log(rank, "eager step done; capturing")
-        graph, mode = None, "eager launches"
-        if args.no_graph:
-            raise_capture = True
-        else:
-            raise_capture = False
-        try:
-            if raise_capture:
-                raise RuntimeError("graph disabled by --no-graph")
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                launch_step()
-            graph, mode = g, "CUDA graph replay of the whole step"
-        except Exception as e:      # capture of the collective is not available: launch eagerly
-            mode = f"eager launches (graph capture failed: {type(e).__name__})"
-            torch.cuda.synchronize()
 
+        def capture(fn):
+            if args.no_graph:
+                return None, "eager launches (graph disabled)"
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    fn()
+                return g, "CUDA graph replay of the whole step"
+            except Exception as e:      # capture of the collective is not available: launch eagerly
+                torch.cuda.synchronize()
+                return None, f"eager launches (graph capture failed: {type(e).__name__})"
+
+        graph, mode = capture(launch_step)
         _log(rank, f"launch mode: {mode}")
 
         def step():
@@ -377,6 +376,18 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             torch.cuda.synchronize()
             dist.barrier()
             torch.cuda.synchronize()
+
+        def timed(fn, reps):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(reps):
+                fn()
+            b.record(stream)
+            barrier()
+            t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
 
         sampler = ClockSampler(local)
         sampler.__enter__()          # samples from warm-up to the end of the timed regions
@@ -391,51 +402,64 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)   # all ranks leave the loop together
             if int(n_extra.item()) == 0:
                 break
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            step()
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
+        ms = timed(step, args.steps)
         # end to end: the step's input vector comes from pinned host memory and the
         # step's output vector goes back to it, inside the timed region
         x_host = x_h.cpu().pin_memory()
-        y_host = torch.empty(H70, dtype=torch.float16).pin_memory()
+        y_host = torch.empty(1, H70, dtype=torch.float16).pin_memory()
+
+        def step_e2e():
+            x_h.copy_(x_host, non_blocking=True)
+            step()
+            y_host.copy_(stack.res, non_blocking=True)
         for _ in range(2):
-            x_h.copy_(x_host, non_blocking=True)
-            step()
-            y_host.copy_(yd, non_blocking=True)
-        barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record(stream)
-        for _ in range(args.steps):
-            x_h.copy_(x_host, non_blocking=True)
-            step()
-            y_host.copy_(yd, non_blocking=True)
-        f1.record(stream)
-        barrier()
-        ms_e2e = f0.elapsed_time(f1)
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
         sampler.__exit__(None, None, None)
         clocks = sampler.summary()
+        launches = stack.launches_per_step
+
+        # beside the headline: the projections alone, and the same stack at batch 32
+        g_proj, _ = capture(projections_only)
+        reps = max(3, args.steps // 4)
+        (g_proj.replay if g_proj is not None else projections_only)()
+        ms_proj = timed(g_proj.replay if g_proj is not None else projections_only, reps) / reps
         phases = None
-        if fused and graph is not None:
-            # where a fused all-reduce launch spends its time: a second graph of the same step,
-            # captured with the library's time stamps switched on, replayed outside the timed region
-            ar.trace(4096)
-            g2 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g2, stream=stream):
-                launch_step()
-            for _ in range(3):
-                g2.replay()
+        if fused and g_proj is not None:
+            # where a fused all-reduce launch spends its time: a graph of the projections-only
+            # pass captured with the library's time stamps switched on, outside the timed regions
+            stack.ar.trace(4096)
+            g2, _ = capture(projections_only)
+            if g2 is not None:
+                for _ in range(3):
+                    g2.replay()
             barrier()
-            phases = ar_phase_table(ar.trace(0), 2 * n_layers)
+            phases = ar_phase_table(stack.ar.trace(0), 2 * n_layers)
             g2 = None
+        g_proj = None
+        batch32 = None
+        try:
+            B = 32
+            s32 = TpLayerStack(cfg, None, rank, world, dev, dist.group.WORLD, allreduce="nccl", batch=B, weights_from=stack)
+            s32.k_cache.copy_(torch.randn(s32.k_cache.shape, generator=gen, device=dev, dtype=torch.float16))
+            s32.v_cache.copy_(torch.randn(s32.v_cache.shape, generator=gen, device=dev, dtype=torch.float16))
+            x32 = (torch.randn(B, H70, generator=gen, device=dev) * 0.5).half()
+            s32.step(x32, KV_LEN - 1)
+            torch.cuda.synchronize()
+            tl.check_device_errors()
+            finite = bool(torch.isfinite(s32.res).all())
+            g32, mode32 = capture(lambda: s32.step(x32, KV_LEN - 1))
+            fn32 = g32.replay if g32 is not None else (lambda: s32.step(x32, KV_LEN - 1))
+            fn32()
+            ms32 = timed(fn32, reps) / reps
+            batch32 = {"ms_per_step": ms32, "tok_per_s": B * 1000.0 / ms32, "allreduce": "NCCL, FP16 [32, 8192]",
+                       "launch": mode32, "finite": finite,
+                       "gemv_route": "tcgen05 GEMM kernel (more than 8 vectors)"}
+            g32 = None
+            s32 = None
+        except Exception as e:          # reported, never fatal for the headline
+            batch32 = {"failed": f"{type(e).__name__}: {e}"[:300]}
     tl.check_device_errors()
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = (float(v) for v in t.tolist())
     if rank == 0:
         peak, peak_kind = measured_peak_hbm()
         value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -445,19 +469,24 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 MMA (exact s32 group sums), f32 accumulate", "data": "synthetic",
-            "config": {"workload": "LLaMA-70B-shape ternary projection stack (hidden 8192, kv 1024, intermediate 28672, %d layers), batch 1, decode-style pass" % n_layers,
-                       "parallelism": f"tp{world}: q/k/v/gate/up column-sharded, o/down row-sharded, all-reduce of the 8192-vector after o and after down (160 per step): " + ("fused into the row-parallel GEMV kernel (peer stores over NVLink, flags, local sum)" if fused else "NCCL"),
-                       "gemv_per_step_per_gpu": launches, "kernel_launches_per_step_per_gpu": 4 * n_layers + (0 if fused else 2 * n_layers),
-                       "bytes_per_step": step_bytes,
+            "config": {"workload": "LLaMA-70B-shape ternary layer stack (hidden 8192, 64 heads / 8 KV heads of 128, intermediate 28672, %d layers): one decode token at batch 1 through norms, q/k/v, RoPE + KV append, attention over a %d-token FP16 KV cache, o, SwiGLU, down" % (n_layers, KV_LEN),
+                       "parallelism": f"tp{world}: q/k/v/gate/up column-sharded (heads and KV cache with them), o/down row-sharded, all-reduce of the 8192-vector after o and after down ({2 * n_layers} per step): " + ("fused into the row-parallel GEMV kernel (peer stores over NVLink, flags, local sum)" if fused else "NCCL"),
+                       "kernel_launches_per_step_per_gpu": launches,
+                       "bytes_per_step": step_bytes, "weight_bytes_per_step": weight_bytes, "kv_bytes_per_step": kv_bytes,
                        "l2": f"{per_gpu_bytes/1e9:.2f} GB of distinct weights per GPU per step (> 126 MB L2), no flush needed",
                        "launch": mode},
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "whole sharded step per GPU (GEMVs + all-reduces)"},
+                         "kernel": "whole sharded step per GPU (GEMVs with all-reduces, attention, norms)"},
             "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": 2 * H70 * world, "d2h_bytes_per_step": 2 * H70 * world,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": 4 * n_layers * args.steps, "clocks": clocks,
+            "gpu_launches": launches * args.steps, "clocks": clocks,
+            "decode": {"batch1": {"ms_per_token": ms / args.steps, "tok_per_s": 1000.0 * args.steps / ms},
+                       "batch32": batch32, "kv_len": KV_LEN},
+            "projections_only": {"ms_per_step": ms_proj, "gbs": weight_bytes / (ms_proj * 1e-3) / 1e9,
+                                 "kernel_launches_per_step_per_gpu": 4 * n_layers + (0 if fused else 2 * n_layers),
+                                 "what": "the seven projections of every layer with their all-reduces, fixed inputs"},
             "parity": parity, "ar_phases_us": phases,
         }), flush=True)
     # Tearing down a process group whose collectives were captured in a CUDA graph can

@@ -51,10 +51,25 @@ int tllm_b200_rope_append(void* q, void* k, const void* v, void* k_cache, void* 
 /* attention_forward, include/kernels.cuh:55-58 (kernels/attention.cu): causal softmax
  * attention with grouped-query heads; query s of the call sits at position
  * kv_len - seq_len + s.  Every seq_len computes the softmax that the reference documents
- * (its multi-token kernel does not: see csrc/attention.cu). */
+ * (its multi-token kernel does not: see csrc/attention.cu).  A single-token call over a
+ * cache of more than 256 positions is split over the cache positions; the partial results
+ * go through a per-device scratch buffer that this call allocates (and grows) on demand --
+ * so the first call with given sizes must not happen during stream capture
+ * (TLLM_ERR_LAUNCH), and calls of one device must be issued in stream order. */
 int tllm_b200_attention(const void* q, const void* k_cache, const void* v_cache, void* output, int batch,
                         int n_heads, int n_kv_heads, int head_dim, int seq_len, int kv_len, int kv_len_max,
                         void* stream);
+
+/* One new token of one sequence: rope_forward on q and k, copy_to_kv_cache of the rotated k
+ * and v at position pos, and attention_forward over positions 0..pos, in ONE launch whose
+ * CTAs each own 64 cache positions of a KV head.  q [n_heads, head_dim] is rotated in place;
+ * k, v [n_kv_heads, head_dim] as the projections wrote them; caches [n_kv_heads, max_seq_len,
+ * head_dim].  No counterpart in the reference (it makes three launches,
+ * src/transformer.cpp:225-245).  Uses the same per-device scratch as tllm_b200_attention:
+ * the first call with given sizes must not happen during stream capture. */
+int tllm_b200_attention_decode(void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* output,
+                               int n_heads, int n_kv_heads, int head_dim, int pos, float theta, int max_seq_len,
+                               void* stream);
 
 /* silu_mul_forward, include/kernels.cuh:60-62 (kernels/activations.cu:18-74). */
 int tllm_b200_silu_mul(const void* gate, const void* up, void* output, int size, void* stream);

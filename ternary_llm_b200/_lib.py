@@ -45,6 +45,7 @@ SIGNATURES = {
     "tllm_b200_copy_to_kv_cache": (_int, [_vp] * 4 + [_int] * 6 + [_vp]),
     "tllm_b200_rope_append": (_int, [_vp] * 5 + [_int] * 6 + [ctypes.c_float, _int, _vp]),
     "tllm_b200_attention": (_int, [_vp] * 4 + [_int] * 7 + [_vp]),
+    "tllm_b200_attention_decode": (_int, [_vp] * 6 + [_int] * 4 + [ctypes.c_float, _int, _vp]),
     "tllm_b200_silu_mul": (_int, [_vp] * 3 + [_int, _vp]),
     "tllm_b200_add": (_int, [_vp] * 3 + [_int, _vp]),
     "tllm_b200_embedding_lookup": (_int, [_vp] * 3 + [_int, _int, _vp]),

@@ -1,5 +1,7 @@
 // extern "C" entry points of the layer operators (include/tllm_b200_layer.h):
 // argument checks and dispatch to layer_ops.cu / attention.cu.
+#include <mutex>
+
 #include "layer.cuh"
 #include "tllm_b200_layer.h"
 
@@ -8,6 +10,51 @@ using namespace tllm;
 namespace {
 inline bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+
+// Scratch of the single-token attention called through the C ABI: the partial results of the
+// splits over cache positions and the per-(sequence, KV head) arrival counters.  One buffer per
+// device, grown on demand; it cannot grow while the stream is being captured into a graph.
+struct AttnScratch {
+    float* ws = nullptr;
+    size_t ws_bytes = 0;
+    unsigned* counters = nullptr;
+    size_t n_counters = 0;
+};
+AttnScratch g_attn[64];
+std::mutex g_attn_mu;
+
+int attention_scratch(size_t ws_bytes, size_t n_counters, cudaStream_t stream, float** ws, unsigned** counters)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(TLLM_ERR_LAUNCH, "attention: no current device");
+    std::lock_guard<std::mutex> lk(g_attn_mu);
+    AttnScratch& s = g_attn[dev];
+    if (s.ws_bytes < ws_bytes || s.n_counters < n_counters) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &cap);
+        if (cap != cudaStreamCaptureStatusNone)
+            return fail(TLLM_ERR_LAUNCH, "attention: the split workspace must grow (%zu bytes); call once with these sizes "
+                        "outside stream capture first", ws_bytes);
+        if (cudaDeviceSynchronize() != cudaSuccess) return fail(TLLM_ERR_LAUNCH, "attention: device synchronize failed");
+        if (s.ws) cudaFree(s.ws);
+        if (s.counters) cudaFree(s.counters);
+        s = AttnScratch();
+        const size_t nb = ws_bytes > s.ws_bytes ? ws_bytes : s.ws_bytes, nc = n_counters > 64 ? n_counters : 64;
+        if (cudaMalloc(&s.ws, nb) != cudaSuccess || cudaMalloc(&s.counters, nc * sizeof(unsigned)) != cudaSuccess ||
+            cudaMemset(s.counters, 0, nc * sizeof(unsigned)) != cudaSuccess) {
+            cudaGetLastError();
+            if (s.ws) cudaFree(s.ws);
+            if (s.counters) cudaFree(s.counters);
+            s = AttnScratch();
+            return fail(TLLM_ERR_LAUNCH, "attention: cannot allocate %zu bytes of split workspace", nb);
+        }
+        s.ws_bytes = nb;
+        s.n_counters = nc;
+    }
+    *ws = s.ws;
+    *counters = s.counters;
+    return TLLM_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -77,8 +124,37 @@ int tllm_b200_attention(const void* q, const void* k_cache, const void* v_cache,
         return fail(TLLM_ERR_ALIGN, "attention: k_cache must be 16-byte aligned");
     int st = check_device();
     if (st) return st;
+    // one token per sequence over a long cache: split the cache positions over CTAs (a single
+    // CTA per KV head walks 2048 positions in about 0.2 ms, far longer than the projections)
+    float* ws = nullptr;
+    unsigned* counters = nullptr;
+    if (seq_len == 1 && batch > 0 && kv_len_max > 256 && n_heads % n_kv_heads == 0) {
+        st = attention_scratch(attention_workspace_bytes(batch, n_heads, n_kv_heads, head_dim, kv_len_max),
+                               (size_t)batch * n_kv_heads, S(stream), &ws, &counters);
+        if (st) return st;
+    }
     return launch_attention((const half*)q, (const half*)k_cache, (const half*)v_cache, (half*)output, batch, n_heads,
-                            n_kv_heads, head_dim, seq_len, kv_len, kv_len_max, nullptr, nullptr, nullptr, S(stream));
+                            n_kv_heads, head_dim, seq_len, kv_len, kv_len_max, nullptr, ws, counters, S(stream));
+}
+
+int tllm_b200_attention_decode(void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* output,
+                               int n_heads, int n_kv_heads, int head_dim, int pos, float theta, int max_seq_len,
+                               void* stream)
+{
+    if (!q || !k || !v || !k_cache || !v_cache || !output) return fail(TLLM_ERR_NULL, "attention_decode: null pointer");
+    if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads || max_seq_len < 1)
+        return fail(TLLM_ERR_SHAPE, "attention_decode: heads=%d/%d max_seq_len=%d", n_heads, n_kv_heads, max_seq_len);
+    if (misaligned(k_cache, 16) || misaligned(v_cache, 16) || misaligned(q, 4) || misaligned(k, 4) || misaligned(v, 4))
+        return fail(TLLM_ERR_ALIGN, "attention_decode: caches must be 16-byte aligned, q/k/v 4-byte aligned");
+    int st = check_device();
+    if (st) return st;
+    float* ws = nullptr;
+    unsigned* counters = nullptr;
+    st = attention_scratch(attention_decode_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq_len), (size_t)n_kv_heads,
+                           S(stream), &ws, &counters);
+    if (st) return st;
+    return launch_attention_decode((half*)q, (const half*)k, (const half*)v, (half*)k_cache, (half*)v_cache, (half*)output,
+                                   n_heads, n_kv_heads, head_dim, max_seq_len, pos, nullptr, theta, ws, counters, S(stream));
 }
 
 int tllm_b200_silu_mul(const void* gate, const void* up, void* output, int size, void* stream)

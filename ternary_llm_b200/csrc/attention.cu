@@ -607,6 +607,47 @@ attention_decode_kernel(const DecodeArgs a)
     if (!s_last) return;
     __threadfence();
     const float* base = a.ws + (size_t)kvh * a.nsplit * rec;
+    if ((rec & 3) == 0 && (hd & 3) == 0 && nactive * 2 * G * (int)sizeof(float) <= 2 * kDecChunk * hd * (int)sizeof(half)) {
+        // A load from another SM's record takes most of a microsecond, so the merge is built
+        // around loads in flight: the splits' (max, sum) pairs go to shared memory first (the
+        // K/V slices there are no longer needed), then every thread owns four channels of one
+        // head and requests their partial outputs of sixteen splits at a time.
+        float* s_ml = smem;                                    // [nactive][2 * G]
+        for (int i = tid; i < nactive * 2 * G; i += kAttnThreads) {
+            const int sp = i / (2 * G), j = i - sp * 2 * G;
+            s_ml[i] = __ldcg(base + (size_t)sp * rec + G * hd + j);
+        }
+        __syncthreads();
+        for (int i4 = tid; i4 < (G * hd) >> 2; i4 += kAttnThreads) {
+            const int g = (i4 << 2) / hd;
+            float mx = -FLT_MAX;
+            for (int sp = 0; sp < nactive; sp++) mx = fmaxf(mx, s_ml[sp * 2 * G + g]);
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
+            for (int s0 = 0; s0 < nactive; s0 += 16) {
+                float4 os[16];
+#pragma unroll
+                for (int u = 0; u < 16; u++)
+                    os[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)min(s0 + u, nactive - 1) * rec) + i4);
+#pragma unroll
+                for (int u = 0; u < 16; u++) {
+                    if (s0 + u < nactive) {
+                        const float w = __expf(s_ml[(s0 + u) * 2 * G + g] - mx);
+                        num.x = fmaf(w, os[u].x, num.x);
+                        num.y = fmaf(w, os[u].y, num.y);
+                        num.z = fmaf(w, os[u].z, num.z);
+                        num.w = fmaf(w, os[u].w, num.w);
+                        den = fmaf(w, s_ml[(s0 + u) * 2 * G + G + g], den);
+                    }
+                }
+            }
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+            half2* o2 = reinterpret_cast<half2*>(op + (size_t)(i4 << 2));
+            o2[0] = __halves2half2(__float2half_rn(num.x * inv), __float2half_rn(num.y * inv));
+            o2[1] = __halves2half2(__float2half_rn(num.z * inv), __float2half_rn(num.w * inv));
+        }
+        return;
+    }
     for (int idx = tid; idx < G * hd; idx += kAttnThreads) {
         const int g = idx / hd;
         float m = -FLT_MAX, num = 0.f, den = 0.f;

@@ -57,6 +57,17 @@ def attention_forward(q, k_cache, v_cache, output, batch: int, n_heads: int, n_k
         batch, n_heads, n_kv_heads, head_dim, seq_len, kv_len, kv_len_max, _stream()))
 
 
+def attention_decode(q, k, v, k_cache, v_cache, output, n_heads: int, n_kv_heads: int, head_dim: int, pos: int,
+                     theta: float, max_seq_len: int) -> None:
+    """One new token of one sequence: rotary embedding, cache append and attention over
+    positions 0..pos in one launch (rope_forward + copy_to_kv_cache + attention_forward)."""
+    _lib.check(_lib.lib().tllm_b200_attention_decode(
+        _chk(q, _H, "q", n_heads * head_dim), _chk(k, _H, "k", n_kv_heads * head_dim), _chk(v, _H, "v", n_kv_heads * head_dim),
+        _chk(k_cache, _H, "k_cache", n_kv_heads * max_seq_len * head_dim),
+        _chk(v_cache, _H, "v_cache", n_kv_heads * max_seq_len * head_dim), _chk(output, _H, "output", n_heads * head_dim),
+        n_heads, n_kv_heads, head_dim, pos, theta, max_seq_len, _stream()))
+
+
 def silu_mul_forward(gate, up, output, size: int) -> None:
     """output = silu(gate) * up (reference include/kernels.cuh:60-62)."""
     _lib.check(_lib.lib().tllm_b200_silu_mul(_chk(gate, _H, "gate"), _chk(up, _H, "up"),

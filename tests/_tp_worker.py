@@ -1,6 +1,7 @@
 """Worker of tests/test_gpu_tp_allreduce.py: one process per GPU (torch.distributed.run).
 Row-parallel GEMV with the all-reduce fused into the kernel, against the oracle and
-against GEMV + NCCL all-reduce."""
+against GEMV + NCCL all-reduce; then the tensor-parallel layer stack (attention included)
+against the unsharded layer oracle."""
 import os
 import sys
 
@@ -63,6 +64,35 @@ def main():
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("TP_ALLREDUCE_OK" if int(flag.item()) == 1 else "TP_ALLREDUCE_FAIL", flush=True)
+
+    # the whole layer stack, heads and intermediate rows split over the ranks, fused exchange:
+    # logits from the replicated residual stream against the unsharded layer oracle
+    from oracle import layer_oracle as LO
+    from ternary_llm_b200 import tllm_format as tf
+    from ternary_llm_b200.tp_stack import StackConfig, TpLayerStack, layer_sources_from_model
+    cfg = tf.TllmConfig(vocab_size=512, hidden_dim=1024, intermediate_dim=2048, n_layers=2, n_heads=8, n_kv_heads=world,
+                        head_dim=128, max_seq_len=32, rope_theta=10000.0, rms_norm_eps=1e-5)
+    model = tf.random_model(cfg, seed=31)                      # the same on every rank
+    sc_ = StackConfig(hidden=cfg.hidden_dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
+                      intermediate=cfg.intermediate_dim, max_seq_len=cfg.max_seq_len, rope_theta=cfg.rope_theta,
+                      rms_norm_eps=cfg.rms_norm_eps)
+    stack = TpLayerStack(sc_, layer_sources_from_model(model, rank, world, dev), rank, world, dev, dist.group.WORLD,
+                         allreduce="fused", batch=1)
+    emb = torch.from_numpy(model.embedding).to(dev)
+    ref = LO.Transformer(model, int8_decode=False)
+    ok2 = True
+    for pos, tok in enumerate([7, 300, 41, 5]):
+        res = stack.step(emb[tok:tok + 1].contiguous(), pos).float().cpu().numpy()
+        want = ref.forward([tok], pos).astype(np.float32)
+        h, _ = LO.rmsnorm(res.astype(np.float16), model.final_norm, cfg.rms_norm_eps)
+        got = LO.fp16_gemv(model.lm_head, h[0]).astype(np.float32)
+        ok2 = ok2 and bool(np.isfinite(res).all()) and bool(np.abs(got - want).max() <= 4e-2 * max(1.0, np.abs(want).max()))
+    tl.check_device_errors()
+    flag2 = torch.tensor([1 if ok2 else 0], device=dev)
+    dist.all_reduce(flag2, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_STACK_OK" if int(flag2.item()) == 1 else "TP_STACK_FAIL", flush=True)
+    flag = torch.minimum(flag, flag2)
     torch.cuda.synchronize()
     dist.barrier()
     os._exit(0 if int(flag.item()) == 1 else 1)

@@ -124,6 +124,34 @@ def test_attention_decode(hq, hk, hd, kv_len):
         assert np.abs(host(out).astype(np.float32) - host(out2).astype(np.float32)).max() <= 4e-3
 
 
+@pytest.mark.parametrize("hq,hk,hd", [(32, 4, 128), (8, 1, 128), (32, 8, 64), (4, 4, 64)])
+@pytest.mark.parametrize("pos,mx", [(0, 64), (63, 64), (64, 300), (2047, 2048), (1000, 2048)])
+def test_fused_single_token_attention_entry_point(hq, hk, hd, pos, mx):
+    """tllm_b200_attention_decode (rotary embedding, cache append and attention in one launch,
+    64 cache positions per CTA, scratch owned by the library) against the three separate
+    operators of the oracle, on the tensor-parallel shard geometries and cache lengths."""
+    rng = np.random.default_rng(hq * 100 + pos)
+    theta = 500000.0
+    q = rng.standard_normal((1, 1, hq, hd)).astype(f16)
+    k = rng.standard_normal((1, 1, hk, hd)).astype(f16)
+    v = rng.standard_normal((1, 1, hk, hd)).astype(f16)
+    kc = np.zeros((1, hk, mx, hd), f16)
+    vc = np.zeros((1, hk, mx, hd), f16)
+    kc[:, :, :pos] = rng.standard_normal((1, hk, pos, hd)).astype(f16)
+    vc[:, :, :pos] = rng.standard_normal((1, hk, pos, hd)).astype(f16)
+    qd, kd, vd, kcd, vcd = dev(q), dev(k), dev(v), dev(kc), dev(vc)
+    out = torch.zeros_like(qd)
+    for _ in range(2):          # a repeated step rewrites the same slot and gives the same output
+        qd.copy_(dev(q))
+        ops.attention_decode(qd, kd, vd, kcd[0], vcd[0], out, hq, hk, hd, pos, theta, mx)
+    qr, kr = LO.rope(q, pos, theta), LO.rope(k, pos, theta)
+    LO.copy_to_kv_cache(kr, v, kc, vc, pos)
+    want = LO.attention(qr, kc, vc, pos + 1)
+    assert np.abs(host(out).astype(np.float32) - want.astype(np.float32)).max() <= 6e-3
+    assert np.abs(host(kcd).astype(np.float32) - kc.astype(np.float32)).max() <= 4e-3 and (host(vcd) == vc).all()
+    tl.check_device_errors()
+
+
 @pytest.mark.parametrize("seq,kv_len", [(2, 2), (33, 33), (16, 300)])
 def test_attention_several_tokens_is_causal_softmax(seq, kv_len):
     rng = np.random.default_rng(seq)
