@@ -155,6 +155,12 @@ int tllm_b200_weight_unregister(const uint32_t* nonzero_masks);
  * _gemv_batched / _gemv_int8.  These kernels keep partial sums of row blocks that
  * span two SMs in a per-device scratch that the library allocates at its first
  * use on a device (make one call per device before capturing a CUDA graph).
+ * FP16 activations are converted per scale group to block fixed point and the
+ * group sums are exact integers: 24 bits below the group's largest magnitude for
+ * one or two vectors per call, 16 bits for passes of three or four vectors (their
+ * rounding error per output is at most 2^-17 * sum over groups of scale * 128 *
+ * max|x| of the group, under half of the 2e-3 * sum|scale * x| bound for any
+ * input); nine vectors and more run on the tcgen05 GEMM kernel in FP16.
  */
 int tllm_b200_gemv_packed(const void* packed, const void* x, void* y,
                           int batch, int rows, int cols, void* stream);

@@ -103,7 +103,9 @@ constexpr int kL2Ahead = TLLM_GEMV_L2_AHEAD_CHUNKS;
 
 // kI8Norm / kI8Silu / kI8Quant: INT8 arithmetic like kI8, but the activation vector is
 // produced inside the kernel's staging phase from FP16 inputs (stage_x_fused below).
-enum Mode { kF16 = 0, kI8 = 2, kI8Norm = 3, kI8Silu = 4, kI8Quant = 5 };
+// kF16W: FP16 activations, four vectors per MMA column block on 16-bit block fixed point (two
+// 8-bit digits per vector) instead of two vectors on 24 bits: batches of three and more.
+enum Mode { kF16 = 0, kF16W = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4, kI8Quant = 5 };
 
 struct GemvArgs {
     const uint8_t* packed;
@@ -424,6 +426,89 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
     }
 }
 
+// kF16W staging: 16-bit block fixed point, q = rint(x * 2^(15-e)) = d0 + 256 d1 with both digits
+// signed bytes (q in [-32896, 32639]: a group whose largest magnitude is within 0.8 % of the
+// next power of two takes one exponent more), four vectors per column block, no pre-scaled
+// steps.  The rounding error per element is at most 2^-17 of the group's largest magnitude:
+// 128 * 2^-17 = 1e-3 of it per group, half of the 2e-3 * sum|scale * x| the benchmark allows
+// even if every other activation of the group were zero.
+//   xdig : uint4 [groups][2 step pairs][NB][8 columns = 4 vectors x 2 digits][4 lanes t]
+//   xcst : uint4 [groups][4 NB] = {f/64, 64 S, 0, 0}, f = 2^(e-15), S = sum(q)
+template <int NB>
+__device__ __forceinline__ void stage_x_f16w(const half* __restrict__ x, int cols, int groups, int batch,
+                                             uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount)
+{
+    constexpr int NVT = NB * 4;
+    const int per_vec = gcount << 4;
+    const int items = per_vec * batch;
+    const int l16 = tid & 15;
+    for (int i = tid; i < gcount * (NVT - batch); i += kThreads) {
+        const int g = i / (NVT - batch), v = batch + i % (NVT - batch);
+        xcst[g * NVT + v] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    const int m = l16 >> 2, j2 = (l16 >> 1) & 1, t0 = 2 * (l16 & 1);
+    const int lane_off = t0 * 4 + (m & 1) * 2 + j2 + (m >> 1) * (NB * 8 * 16);     // words, inside a group's entry
+    auto fetch = [&](int item) {
+        const int b = (int)((unsigned)item / (unsigned)per_vec);
+        const int el = item - b * per_vec;
+        int gg = g0 + (el >> 4);
+        if (gg >= groups) gg -= groups;
+        return __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16);
+    };
+    int item = tid;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (item < items) raw = fetch(item);
+    for (; (item & ~31) < items; item += kThreads) {
+        const bool valid = item < items;
+        const uint4 cur = raw;
+        if (item + kThreads < items) raw = fetch(item + kThreads);
+        const int b = valid ? (int)((unsigned)item / (unsigned)per_vec) : 0;
+        const int g = ((valid ? item : 0) - b * per_vec) >> 4;
+        uint32_t mb = __vmaxu2(__vmaxu2(cur.x & 0x7fff7fffu, cur.y & 0x7fff7fffu),
+                               __vmaxu2(cur.z & 0x7fff7fffu, cur.w & 0x7fff7fffu));
+        mb = max(mb & 0xffffu, mb >> 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+        const bool finite = mb < 0x7c00u;
+        const bool live = finite && mb != 0u;
+        const int e = (int)max(mb >> 10, 1u) - 14 + ((mb & 0x3ffu) >= 1016u ? 1 : 0);
+        const float up = live ? __uint_as_float((uint32_t)(15 - e + 127) << 23) : 0.f;
+        const float dn = finite ? (mb != 0u ? __uint_as_float((uint32_t)(e - 15 + 127) << 23) : 0.f)
+                                : __uint_as_float(0x7fc00000u);
+        // u = q + 32896: its two bytes are the digits plus 128
+        uint32_t u[8];
+        {
+            const uint32_t rw[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rw[i]));
+                u[2 * i] = __float_as_uint(fmaf(f.x, up, 12582912.0f)) - 0x4b400000u + 32896u;
+                u[2 * i + 1] = __float_as_uint(fmaf(f.y, up, 12582912.0f)) - 0x4b400000u + 32896u;
+            }
+        }
+        uint32_t w[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t a = __byte_perm(u[4 * h], u[4 * h + 1], 0x5140), c = __byte_perm(u[4 * h + 2], u[4 * h + 3], 0x5140);
+            w[h][0] = __byte_perm(a, c, 0x5410) ^ 0x80808080u;
+            w[h][1] = __byte_perm(a, c, 0x7632) ^ 0x80808080u;
+        }
+        int sq = __dp4a((int)w[1][0], 0x01010101, __dp4a((int)w[0][0], 0x01010101, 0)) +
+                 256 * __dp4a((int)w[1][1], 0x01010101, __dp4a((int)w[0][1], 0x01010101, 0));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (valid) {
+            const int beta = b >> 2, vl = b & 3;
+            uint32_t* p = xdig + ((g * 2 * NB + beta) * 8 + vl * 2) * 16 + lane_off;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int d = 0; d < 2; d++) p[(d * 4 + h) * 4] = w[h][d];
+            if (l16 == 0) xcst[g * NVT + b] = make_uint4(__float_as_uint(dn * 0.015625f), (uint32_t)(sq * 64), 0u, 0u);
+        }
+    }
+}
+
 // INT8 activations in shared memory: two digit columns, x = lo + 16 hi with lo = x & 15 (0..15)
 // and hi = x >> 4 (-8..7), laid out like the FP16 digits: uint4 [groups][2 step pairs][2 columns]
 // [4 lanes t], words (b0,b1) of step 2p and (b0,b1) of step 2p+1, the even step times 4.
@@ -618,8 +703,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu || MODE == kI8Quant);
     constexpr bool I8 = (MODE == kI8 || FUSEDX);
+    constexpr bool W16 = (MODE == kF16W);         // four vectors per column block, two 8-bit digits each
     constexpr int NVT = NB * NV;                  // vectors per weight pass
     static_assert(!I8 || (NB == 1 && NV == 1), "INT8 modes carry one vector");
+    static_assert(!W16 || NV == 4, "the wide FP16 mode carries four vectors per column block");
 
     if (!a.late_release) asm volatile("griddepcontrol.launch_dependents;");
 
@@ -713,8 +800,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         stage_x_i8(reinterpret_cast<const int8_t*>(a.x), a.cols, xstage, sx, tid);
     } else {
         const int g0 = a.x_local ? (int)((unsigned)t0 % (unsigned)G) : 0;
-        stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
-                            a.x_local ? n : G);
+        if constexpr (W16)
+            stage_x_f16w<NB>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
+                             a.x_local ? n : G);
+        else
+            stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
+                                a.x_local ? n : G);
     }
     __syncthreads();
     TL(3);
@@ -728,12 +819,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     // B operand entry of this lane: column gq -> FP16 (vector gq / 4 of the block, digit gq % 4),
     // INT8 digit gq; lanes of columns that carry nothing read a neighbour's entry, their products
     // are unused.  Shared-memory addresses are kept as 32-bit numbers.
-    const int bcol = I8 ? min(gq, 1) : (min(gq >> 2, NV - 1) * 4 + (gq & 3));
-    constexpr int kXbStride = I8 ? 8 : NV * 16;                 // entries per (group, step pair, block)
+    const int bcol = I8 ? min(gq, 1) : (W16 ? gq : (min(gq >> 2, NV - 1) * 4 + (gq & 3)));
+    constexpr int kXbStride = I8 ? 8 : (W16 ? 32 : NV * 16);    // entries per (group, step pair, block)
     constexpr uint32_t kXgBytes = 2u * NB * kXbStride * 16u;    // staged bytes per group
     const uint32_t xb_addr = smem_addr(xstage) + (uint32_t)(bcol * 4 + t) * 16u;
     // group constants of this lane: FP16 {factor, offset} pair (first pair for even t, second for odd)
-    const uint32_t xc_addr = smem_addr(smem + a.off_xcst) + (I8 ? 0u : (uint32_t)(t & 1) * 8u);
+    const uint32_t xc_addr = smem_addr(smem + a.off_xcst) + ((I8 || W16) ? 0u : (uint32_t)(t & 1) * 8u);
     const uint32_t sc_off = kTileCodeBytes + (uint32_t)gq * 4u;      // this lane's two scales inside a tile
     const bool xloc = !I8 && a.x_local;
 
@@ -756,10 +847,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 float v = acc[b][h];
-                if (!I8) v += __shfl_xor_sync(0xffffffffu, v, 1);   // lanes t, t^1: the digit halves of one vector
+                if (!I8 && !W16) v += __shfl_xor_sync(0xffffffffu, v, 1);   // lanes t, t^1: the digit halves of one vector
                 const int row = gq + 8 * h;
                 if (I8) {
                     if (t == 0) pu[row] = v;
+                } else if (W16) {
+                    pu[row * NVT + b * 4 + t] = v;                  // lane t holds vector t of the block
                 } else if ((t & 1) == 0 && (t >> 1) < NV) {
                     pu[row * NVT + b * NV + (t >> 1)] = v;
                 }
@@ -778,13 +871,31 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
             const uint32_t xa = xb_addr + (uint32_t)gx * kXgBytes + (uint32_t)b * (kXbStride * 16u);
             const uint4 xb0 = lds128(xa);
             const uint4 xb1 = lds128(xa + NB * kXbStride * 16u);
+            int p0, p1;
+            float fx;
+            if constexpr (W16) {
+                // four independent MMAs, one per 32-column step; step f carries the factor 4^f of
+                // its bit field, so ((D0*4 + D1)*4 + D2)*4 + D3 = 64 * (sum over the group) per
+                // column; columns 2t, 2t+1 are the low and the high digit of vector t
+                int d0[4], d1[4], d2[4], d3[4];
+                imma<true>(d0, wd.x & 0x03030303u, wd.z & 0x03030303u, wd.y & 0x03030303u, wd.w & 0x03030303u, xb0.x, xb0.y);
+                imma<true>(d1, wd.x & 0x0c0c0c0cu, wd.z & 0x0c0c0c0cu, wd.y & 0x0c0c0c0cu, wd.w & 0x0c0c0c0cu, xb0.z, xb0.w);
+                imma<true>(d2, wd.x & 0x30303030u, wd.z & 0x30303030u, wd.y & 0x30303030u, wd.w & 0x30303030u, xb1.x, xb1.y);
+                imma<true>(d3, wd.x & 0xc0c0c0c0u, wd.z & 0xc0c0c0c0u, wd.y & 0xc0c0c0c0u, wd.w & 0xc0c0c0c0u, xb1.z, xb1.w);
+                int q[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) q[i] = ((d0[i] * 4 + d1[i]) * 4 + d2[i]) * 4 + d3[i];
+                const uint2 c = lds64(xc_addr + (uint32_t)(gx * NVT + b * 4 + t) * 16u);
+                fx = __uint_as_float(c.x);
+                p0 = q[1] * 256 + q[0] - (int)c.y;
+                p1 = q[3] * 256 + q[2] - (int)c.y;
+            } else {
             int lo[4], hi[4];
             // words (h, j2) = (0,0) (0,1) (1,0) (1,1) are registers a0, a2, a1, a3
             imma<true>(lo, wd.x & 0x03030303u, wd.z & 0x03030303u, wd.y & 0x03030303u, wd.w & 0x03030303u, xb0.x, xb0.y);
             imma<true>(hi, wd.x & 0x30303030u, wd.z & 0x30303030u, wd.y & 0x30303030u, wd.w & 0x30303030u, xb1.x, xb1.y);
             imma<false>(lo, wd.x & 0x0c0c0c0cu, wd.z & 0x0c0c0c0cu, wd.y & 0x0c0c0c0cu, wd.w & 0x0c0c0c0cu, xb0.z, xb0.w);
             imma<false>(hi, wd.x & 0xc0c0c0c0u, wd.z & 0xc0c0c0c0u, wd.y & 0xc0c0c0c0u, wd.w & 0xc0c0c0c0u, xb1.z, xb1.w);
-            float fx;
             int soff;
             if (I8) {
                 fx = 1.0f;
@@ -796,8 +907,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
                 soff = (int)c.y;
             }
             // lo = 4 * (steps 0,1), hi = 64 * (steps 2,3): lo * 16 + hi = 64 * (sum of the group) per column
-            const int p0 = (lo[1] * 16 + hi[1]) * kMulA + (lo[0] * 16 + hi[0]) - soff;
-            const int p1 = (lo[3] * 16 + hi[3]) * kMulA + (lo[2] * 16 + hi[2]) - soff;
+            p0 = (lo[1] * 16 + hi[1]) * kMulA + (lo[0] * 16 + hi[0]) - soff;
+            p1 = (lo[3] * 16 + hi[3]) * kMulA + (lo[2] * 16 + hi[2]) - soff;
+            }
             acc[b][0] = fmaf((float)p0, sc.x * fx, acc[b][0]);
             acc[b][1] = fmaf((float)p1, sc.y * fx, acc[b][1]);
         }
@@ -1224,7 +1336,9 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
         *n_max_out = n_max;
         a.x_local = (!i8 && n_max < a.groups) ? 1 : 0;
         const int gstaged = a.x_local ? n_max : a.groups;
-        size_t off = i8 ? (size_t)cols * 2 : (size_t)gstaged * nvt * 512;
+        // staged activations: INT8 two digit columns; FP16 512 bytes per group and vector on 24
+        // bits, 1 KB per group for the four vectors of the wide mode
+        size_t off = i8 ? (size_t)cols * 2 : (mode == kF16W ? (size_t)gstaged * 1024 : (size_t)gstaged * nvt * 512);
         off = (off + 15) & ~(size_t)15;
         a.off_xcst = (int)off;
         off += i8 ? (size_t)a.groups * sizeof(int) : (size_t)gstaged * nvt * 16;
@@ -1324,14 +1438,16 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
 
 // Vectors per pass as instantiated for a batch of 1..4 FP16 vectors.
 static inline int f16_nvt(int batch) { return batch <= 1 ? 1 : (batch == 2 ? 2 : 4); }
+// FP16 vectors: one or two ride the 24-bit digits, three and four the wide 16-bit mode
+static inline int f16_mode(int mode, int batch) { return (mode == kF16 && batch >= 3) ? kF16W : mode; }
 
 static int dispatch(const GemvArgs& a, int mode, int grid, size_t smem, cudaStream_t stream)
 {
     switch (mode) {
         case kF16:
             if (a.batch <= 1) return launch_mode<kF16, 1, 1>(a, grid, smem, stream);
-            if (a.batch == 2) return launch_mode<kF16, 1, 2>(a, grid, smem, stream);
-            return launch_mode<kF16, 2, 2>(a, grid, smem, stream);
+            return launch_mode<kF16, 1, 2>(a, grid, smem, stream);
+        case kF16W: return launch_mode<kF16W, 1, 4>(a, grid, smem, stream);
         case kI8Norm: return launch_mode<kI8Norm, 1, 1>(a, grid, smem, stream);
         case kI8Silu: return launch_mode<kI8Silu, 1, 1>(a, grid, smem, stream);
         case kI8Quant: return launch_mode<kI8Quant, 1, 1>(a, grid, smem, stream);
@@ -1389,7 +1505,9 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     a.batch = batch;
     int grid = 0;
     size_t smem = 0;
-    if ((st = plan_gemv(a, s->sms, mode, mode == kF16 ? f16_nvt(batch) : 1, kMaxCtas, false, &grid, &smem))) return st;
+    mode = f16_mode(mode, batch);
+    if ((st = plan_gemv(a, s->sms, mode, (mode == kF16 || mode == kF16W) ? f16_nvt(batch) : 1, kMaxCtas, false, &grid, &smem)))
+        return st;
     unsigned ticket;
     {
         std::lock_guard<std::mutex> lk(g_mu);

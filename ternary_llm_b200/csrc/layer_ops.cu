@@ -551,50 +551,79 @@ int launch_fp16_gemv_batched(const half* w, const half* x, half* y, int batch, i
 // ---------------------------------------------------------------------------
 // FP16 GEMM   C[M, N] = A[M, K] . B[N, K]^T, FP32 accumulation   reference: kernels/elementwise.cu:216-304
 // ---------------------------------------------------------------------------
-// Off the decode path (the engine calls it only for an FP16 lm_head over several
-// tokens, which its forward pass never requests): a plain 64x64x16 shared-memory tiling.
-__global__ void __launch_bounds__(256)
+// Off the decode path (the engine calls it only for an FP16 lm_head over several tokens,
+// which its forward pass never requests).  C[M,N] = A[M,K] . B[N,K]^T on mma.sync.m16n8k16:
+// A is row-major along K and B[N,K] is exactly the "col" operand, so every lane loads its
+// operand fragments straight from global memory as 32-bit words (two consecutive K values of
+// one row) -- no shared memory, no transposition.  A CTA of four warps owns 64 x 64 of C, a
+// warp 32 x 32 (2 x 4 MMA tiles, FP32 accumulators).  Edges and odd K go through guarded
+// element loads.
+__device__ __forceinline__ uint32_t gemm_pair(const half* __restrict__ p, int row, int rows, int k, int K, bool vec)
+{
+    if (row >= rows) return 0u;
+    const half* q = p + (size_t)row * K + k;
+    if (vec && k + 1 < K) return __ldg(reinterpret_cast<const unsigned int*>(q));
+    const unsigned short lo = (k < K) ? __half_as_ushort(q[0]) : (unsigned short)0;
+    const unsigned short hi = (k + 1 < K) ? __half_as_ushort(q[1]) : (unsigned short)0;
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+__global__ void __launch_bounds__(128)
 fp16_gemm_kernel(const half* __restrict__ A, const half* __restrict__ B, half* __restrict__ C, int M, int N, int K)
 {
-    __shared__ float sa[16][64 + 1], sb[16][64 + 1];
     pdl_launch_dependents();
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    float acc[4][4] = {};
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gq = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.y * 64 + (warp >> 1) * 32, n0 = blockIdx.x * 64 + (warp & 1) * 32;
+    // 32-bit loads need an even K (rows then start on 4-byte boundaries) and aligned bases
+    const bool vec = (K & 1) == 0 && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 3) == 0;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f;
     pdl_wait();
     for (int k0 = 0; k0 < K; k0 += 16) {
-        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
-            const int r = i >> 4, c = i & 15;
-            sa[c][r] = (m0 + r < M && k0 + c < K) ? __half2float(A[(size_t)(m0 + r) * K + k0 + c]) : 0.f;
-            sb[c][r] = (n0 + r < N && k0 + c < K) ? __half2float(B[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+        uint32_t a[2][4], b[4][2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int r = m0 + i * 16 + gq;
+            a[i][0] = gemm_pair(A, r, M, k0 + 2 * t, K, vec);
+            a[i][1] = gemm_pair(A, r + 8, M, k0 + 2 * t, K, vec);
+            a[i][2] = gemm_pair(A, r, M, k0 + 2 * t + 8, K, vec);
+            a[i][3] = gemm_pair(A, r + 8, M, k0 + 2 * t + 8, K, vec);
         }
-        __syncthreads();
 #pragma unroll
-        for (int kk = 0; kk < 16; kk++) {
-            float a[4], b[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                a[i] = sa[kk][ty * 4 + i];
-                b[i] = sb[kk][tx * 4 + i];
-            }
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-        }
-        __syncthreads();
-    }
-    for (int i = 0; i < 4; i++)
         for (int j = 0; j < 4; j++) {
-            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-            if (m < M && n < N) C[(size_t)m * N + n] = __float2half_rn(acc[i][j]);
+            const int c = n0 + j * 8 + gq;
+            b[j][0] = gemm_pair(B, c, N, k0 + 2 * t, K, vec);
+            b[j][1] = gemm_pair(B, c, N, k0 + 2 * t + 8, K, vec);
         }
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                    : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
+                    : "r"(a[i][0]), "r"(a[i][1]), "r"(a[i][2]), "r"(a[i][3]), "r"(b[j][0]), "r"(b[j][1]));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int m = m0 + i * 16 + gq + (e >> 1) * 8, n = n0 + j * 8 + 2 * t + (e & 1);
+                if (m < M && n < N) C[(size_t)m * N + n] = __float2half_rn(acc[i][j][e]);
+            }
 }
 
 int launch_fp16_gemm(const half* A, const half* B, half* C, int M, int N, int K, cudaStream_t stream)
 {
     if (M == 0 || N == 0) return TLLM_OK;
-    return launch_pdl("fp16_gemm", fp16_gemm_kernel, dim3((N + 63) / 64, (M + 63) / 64), dim3(256), 0, stream, A, B, C,
+    return launch_pdl("fp16_gemm", fp16_gemm_kernel, dim3((N + 63) / 64, (M + 63) / 64), dim3(128), 0, stream, A, B, C,
                       M, N, K);
 }
 
