@@ -83,6 +83,9 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
 // A ring that two co-resident CTAs allow but that holds fewer slots than this (and less than the
 // CTA's whole share) is given up for one CTA per SM with all of the shared memory.
+#ifndef TLLM_GEMV_PAIR_STAGING
+#define TLLM_GEMV_PAIR_STAGING 1
+#endif
 #ifndef TLLM_GEMV_MIN_SHARED_SLOTS
 #define TLLM_GEMV_MIN_SHARED_SLOTS 24
 #endif
@@ -137,6 +140,8 @@ struct GemvArgs {
                             //    wait instead of at its start (see release_rule)
     int ring_slots;         // R
     int l2_prefetch;        // 1: warps prefetch into L2 the chunks beyond what the ring holds
+    int pair;               // FP16 modes: 1 = launched as clusters of two CTAs that stage half of the activations
+                            // each and write their digits into both CTAs' shared memory
     int x_local;            // FP16 modes, CTAs with fewer tiles than a row has groups: a CTA stages only
                             // the groups it walks (a cyclic run starting at its first tile's group)
     uint2* ws;              // [gridDim.x][2][ws_stride / 2] partial records {value, flag} of this ticket,
@@ -239,6 +244,30 @@ __device__ __forceinline__ void fill_slot(uint32_t d, const uint8_t* s, uint32_t
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Cluster of two CTAs: rank of this CTA, the partner's address of one of my shared-memory
+// addresses, a 32-bit store there, and the cluster-wide barrier (every thread of both CTAs).
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_peer(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Shared-memory loads by 32-bit shared address.
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
 {
@@ -337,9 +366,13 @@ __device__ __forceinline__ void quad_digits(uint32_t u0, uint32_t u1, uint32_t u
 // half-warp cover one scale group and agree on its exponent and sums with shuffles.
 // The groups staged are the cyclic run g0, g0+1, ... (mod groups) of length gcount; staged
 // group number i of that run is stored at index i (gcount == groups, g0 == 0: all of them).
+// part / nparts / peer: with nparts == 2 this CTA converts every second batch of kThreads items
+// (those of parity `part`) and stores each result word to its own shared memory and, at `peer`
+// (the partner's address of xdig; the constants follow at the same distance), to the partner's.
 template <int NB, int NV>
 __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols, int groups, int batch,
-                                            uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount)
+                                            uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount,
+                                            int part = 0, int nparts = 1, uint32_t peer = 0)
 {
     constexpr int NVT = NB * NV;
     const int per_vec = gcount << 4;               // 8-element items per vector (16 per group)
@@ -364,13 +397,14 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
         if (gg >= groups) gg -= groups;
         return __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16);
     };
-    int item = tid;
+    const int stride = kThreads * nparts;
+    int item = tid + part * kThreads;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (item < items) raw = fetch(item);
-    for (; (item & ~31) < items; item += kThreads) {          // warp-uniform: the shuffles need every lane
+    for (; (item & ~31) < items; item += stride) {            // warp-uniform: the shuffles need every lane
         const bool valid = item < items;
         const uint4 cur = raw;
-        if (item + kThreads < items) raw = fetch(item + kThreads);      // in flight during this item's arithmetic
+        if (item + stride < items) raw = fetch(item + stride);          // in flight during this item's arithmetic
         const int b = (NVT == 1 || !valid) ? 0 : (int)((unsigned)item / (unsigned)per_vec);
         const int g = ((valid ? item : 0) - b * per_vec) >> 4;          // staged group number
         // largest magnitude of the group as an FP16 bit pattern: orders finite values,
@@ -414,14 +448,27 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
         }
         if (valid) {
             const int beta = (NV == 2) ? (b >> 1) : 0, vl = (NV == 2) ? (b & 1) : 0;
-            uint32_t* p = xdig + ((g * 2 * NB + beta) * (NV * 4) + vl * 4) * 16 + lane_off;
+            const int pw = ((g * 2 * NB + beta) * (NV * 4) + vl * 4) * 16 + lane_off;
+            uint32_t* p = xdig + pw;
 #pragma unroll
             for (int h = 0; h < 2; h++)             // second quad: next lane t
 #pragma unroll
-                for (int d = 0; d < 4; d++) p[(d * 4 + h) * 4] = w[h][d];
-            if (l16 == 0)
-                xcst[g * NVT + b] = make_uint4(__float_as_uint(dn * 0.015625f), (uint32_t)(slo * 64),
-                                               __float_as_uint(dn * 64.0f), (uint32_t)(shi * 64));
+                for (int d = 0; d < 4; d++) {
+                    p[(d * 4 + h) * 4] = w[h][d];
+                    if (nparts > 1) st_peer(peer + (uint32_t)(pw + (d * 4 + h) * 4) * 4u, w[h][d]);
+                }
+            if (l16 == 0) {
+                const uint4 c = make_uint4(__float_as_uint(dn * 0.015625f), (uint32_t)(slo * 64),
+                                           __float_as_uint(dn * 64.0f), (uint32_t)(shi * 64));
+                xcst[g * NVT + b] = c;
+                if (nparts > 1) {
+                    const uint32_t pc = peer + (uint32_t)(reinterpret_cast<uint8_t*>(xcst + g * NVT + b) - reinterpret_cast<uint8_t*>(xdig));
+                    st_peer(pc, c.x);
+                    st_peer(pc + 4, c.y);
+                    st_peer(pc + 8, c.z);
+                    st_peer(pc + 12, c.w);
+                }
+            }
         }
     }
 }
@@ -436,7 +483,8 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
 //   xcst : uint4 [groups][4 NB] = {f/64, 64 S, 0, 0}, f = 2^(e-15), S = sum(q)
 template <int NB>
 __device__ __forceinline__ void stage_x_f16w(const half* __restrict__ x, int cols, int groups, int batch,
-                                             uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount)
+                                             uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount,
+                                             int part = 0, int nparts = 1, uint32_t peer = 0)
 {
     constexpr int NVT = NB * 4;
     const int per_vec = gcount << 4;
@@ -455,13 +503,14 @@ __device__ __forceinline__ void stage_x_f16w(const half* __restrict__ x, int col
         if (gg >= groups) gg -= groups;
         return __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16);
     };
-    int item = tid;
+    const int stride = kThreads * nparts;
+    int item = tid + part * kThreads;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (item < items) raw = fetch(item);
-    for (; (item & ~31) < items; item += kThreads) {
+    for (; (item & ~31) < items; item += stride) {
         const bool valid = item < items;
         const uint4 cur = raw;
-        if (item + kThreads < items) raw = fetch(item + kThreads);
+        if (item + stride < items) raw = fetch(item + stride);
         const int b = valid ? (int)((unsigned)item / (unsigned)per_vec) : 0;
         const int g = ((valid ? item : 0) - b * per_vec) >> 4;
         uint32_t mb = __vmaxu2(__vmaxu2(cur.x & 0x7fff7fffu, cur.y & 0x7fff7fffu),
@@ -499,12 +548,24 @@ __device__ __forceinline__ void stage_x_f16w(const half* __restrict__ x, int col
         for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         if (valid) {
             const int beta = b >> 2, vl = b & 3;
-            uint32_t* p = xdig + ((g * 2 * NB + beta) * 8 + vl * 2) * 16 + lane_off;
+            const int pw = ((g * 2 * NB + beta) * 8 + vl * 2) * 16 + lane_off;
+            uint32_t* p = xdig + pw;
 #pragma unroll
             for (int h = 0; h < 2; h++)
 #pragma unroll
-                for (int d = 0; d < 2; d++) p[(d * 4 + h) * 4] = w[h][d];
-            if (l16 == 0) xcst[g * NVT + b] = make_uint4(__float_as_uint(dn * 0.015625f), (uint32_t)(sq * 64), 0u, 0u);
+                for (int d = 0; d < 2; d++) {
+                    p[(d * 4 + h) * 4] = w[h][d];
+                    if (nparts > 1) st_peer(peer + (uint32_t)(pw + (d * 4 + h) * 4) * 4u, w[h][d]);
+                }
+            if (l16 == 0) {
+                const uint32_t c0 = __float_as_uint(dn * 0.015625f), c1 = (uint32_t)(sq * 64);
+                xcst[g * NVT + b] = make_uint4(c0, c1, 0u, 0u);
+                if (nparts > 1) {
+                    const uint32_t pc = peer + (uint32_t)(reinterpret_cast<uint8_t*>(xcst + g * NVT + b) - reinterpret_cast<uint8_t*>(xdig));
+                    st_peer(pc, c0);
+                    st_peer(pc + 4, c1);
+                }
+            }
         }
     }
 }
@@ -779,6 +840,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         for (int c = cinit; c < min(nchunks, cinit + kL2Ahead); c++) l2_chunk(c);
     const uint8_t* src_next = src_lane + (size_t)cinit * kSlotBytes;      // the next chunk to request
     __syncwarp();
+    // paired launch: the partner's shared memory may be written once both CTAs are running
+    const bool paired = !I8 && !AR && a.pair;
+    if (paired) cluster_barrier();
     TL(1);
 
     // ---- everything below may depend on the previous kernel in the stream -------
@@ -800,14 +864,22 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         stage_x_i8(reinterpret_cast<const int8_t*>(a.x), a.cols, xstage, sx, tid);
     } else {
         const int g0 = a.x_local ? (int)((unsigned)t0 % (unsigned)G) : 0;
+        const int part = paired ? (int)cluster_rank() : 0, nparts = paired ? 2 : 1;
+        const uint32_t peer = paired ? peer_addr(smem_addr(xstage), (uint32_t)(part ^ 1)) : 0u;
         if constexpr (W16)
             stage_x_f16w<NB>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
-                             a.x_local ? n : G);
+                             a.x_local ? n : G, part, nparts, peer);
         else
             stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
-                                a.x_local ? n : G);
+                                a.x_local ? n : G, part, nparts, peer);
     }
-    __syncthreads();
+    // both halves of a paired launch are in place (and no store to the partner is outstanding)
+    // once every thread of the two CTAs has passed this barrier; it orders the CTA's own
+    // shared-memory writes like __syncthreads()
+    if (paired)
+        cluster_barrier();
+    else
+        __syncthreads();
     TL(3);
 
     // ---- per-lane constants ------------------------------------------------------
@@ -1388,7 +1460,17 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
         return fail(TLLM_ERR_SIZE, "rows=%d cols=%d with %d vectors per pass needs more shared memory than an SM has "
                     "(%zu bytes before the ring)", rows, cols, nvt, off);
     a.ring_slots = (int)slots;
-    a.l2_prefetch = (chunks_of(n_max) > (int)slots) ? 1 : 0;
+    // Staging shared by pairs of CTAs (clusters of two; each converts half of the activations and
+    // writes into both shared memories): for passes of three and four vectors, where every thread
+    // converts several 8-element items (measured: 14336x4096 at four vectors 9.2 -> 8.3 us,
+    // 4096x14336 16.4 -> 13.7 us).  One vector of a long row gains nothing: 4096x14336 9.4 us
+    // either way, the stores into the partner's shared memory and the two cluster barriers cost
+    // what the halved conversion saves.
+    a.pair = (TLLM_GEMV_PAIR_STAGING && !i8 && !a.x_local && (grid % 2) == 0 && a.batch >= 3 &&
+              (long long)a.groups * 16 * a.batch >= 2 * kThreads) ? 1 : 0;
+    // only where the ring is shallow (fewer than two slots per warp): a deeper ring hides the HBM
+    // latency by itself and the prefetch instructions then only cost issue slots
+    a.l2_prefetch = (chunks_of(n_max) > (int)slots && slots < 2 * kWarps) ? 1 : 0;
     off += (size_t)slots * kSlotBytes;
     *grid_out = grid;
     *smem_out = off;
@@ -1423,11 +1505,18 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
+    if (a.pair) {       // clusters of two CTAs (plan_gemv made the grid even)
+        at[1].id = cudaLaunchAttributeClusterDimension;
+        at[1].val.clusterDim.x = 2;
+        at[1].val.clusterDim.y = 1;
+        at[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_packed_kernel<MODE, NB, NV, AR>, a);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -1685,6 +1774,7 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     int grid = 0;
     size_t smem = 0;
     if ((st = plan_gemv(a, nd->sms, kF16, 1, kNoAllocMaxCtas, false, &grid, &smem))) return st;
+    a.pair = 0;                         // this entry point keeps to plain launches
     a.ws = reinterpret_cast<uint2*>(nd->base);
     a.err = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
     a.ws_stride = 2 * kTileRows;
@@ -1753,6 +1843,7 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
     int grid = 0;
     size_t smem = 0;
     if ((st = plan_gemv(a, s->sms, kF16, 1, kMaxCtas, true, &grid, &smem))) return st;
+    a.pair = 0;                         // the all-reduce instantiation stages on its own
     a.ws = s->ws;                       // unused in the aligned split
     a.err = s->misc + 1;
     a.ws_stride = 2 * kRecFloats;
