@@ -319,6 +319,10 @@ struct DecodeArgs {
     int* err;
 };
 
+// kLong: built with the staged merge for more than 16 splits (a cache of more than 1024
+// positions); the short instantiation is the kernel without it (fewer registers, and measured
+// quicker on short caches).
+template <bool kLong>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_decode_kernel(const DecodeArgs a)
 {
@@ -607,7 +611,7 @@ attention_decode_kernel(const DecodeArgs a)
     if (!s_last) return;
     __threadfence();
     const float* base = a.ws + (size_t)kvh * a.nsplit * rec;
-    if (nactive > 16 && (rec & 3) == 0 && (hd & 3) == 0 &&
+    if (kLong && nactive > 16 && (rec & 3) == 0 && (hd & 3) == 0 &&
         nactive * 2 * G * (int)sizeof(float) <= 2 * kDecChunk * hd * (int)sizeof(half)) {
         // Many splits (a long cache; with 16 or fewer the loop below is quicker, measured on the
         // 1B decode step: 0.632 against 0.651 ms per token).  A load from another SM's record
@@ -730,10 +734,14 @@ int launch_attention_decode(half* q, const half* k, const half* v, half* k_cache
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr[dev]) {
-        cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr[dev] = true;
     }
-    return launch_pdl("attention_decode", attention_decode_kernel, dim3(a.nsplit, n_kv_heads), dim3(kAttnThreads), smem,
+    if (a.nsplit > 16)
+        return launch_pdl("attention_decode", attention_decode_kernel<true>, dim3(a.nsplit, n_kv_heads), dim3(kAttnThreads),
+                          smem, stream, a);
+    return launch_pdl("attention_decode", attention_decode_kernel<false>, dim3(a.nsplit, n_kv_heads), dim3(kAttnThreads), smem,
                       stream, a);
 }
 
