@@ -86,6 +86,12 @@ constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
 #ifndef TLLM_GEMV_PAIR_STAGING
 #define TLLM_GEMV_PAIR_STAGING 1
 #endif
+#ifndef TLLM_GEMV_KSPLIT
+#define TLLM_GEMV_KSPLIT 1
+#endif
+#ifndef TLLM_GEMV_KSPLIT_MIN_COLS
+#define TLLM_GEMV_KSPLIT_MIN_COLS 12288
+#endif
 #ifndef TLLM_GEMV_MIN_SHARED_SLOTS
 #define TLLM_GEMV_MIN_SHARED_SLOTS 24
 #endif
@@ -140,6 +146,11 @@ struct GemvArgs {
                             //    wait instead of at its start (see release_rule)
     int ring_slots;         // R
     int l2_prefetch;        // 1: warps prefetch into L2 the chunks beyond what the ring holds
+    int ksplit;             // 1 = clusters of two CTAs share whole row blocks, each CTA contracting one half of
+                            // the columns (and staging only that half of the activations); the halves' sums
+                            // meet in the shared memory of the cluster's first CTA.  part_q/part_r then
+                            // partition the row blocks over the clusters
+    int off_pairbuf;        // shared memory: float [2][row blocks of the cluster][16] of that exchange
     int pair;               // FP16 modes: 1 = launched as clusters of two CTAs that stage half of the activations
                             // each and write their digits into both CTAs' shared memory
     int x_local;            // FP16 modes, CTAs with fewer tiles than a row has groups: a CTA stages only
@@ -758,7 +769,9 @@ __device__ __forceinline__ half* out_ptr(const GemvArgs& a, int b, int r)
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
-template <int MODE, int NB, int NV, bool AR>
+// KS: the column split inside clusters of two CTAs (GemvArgs::ksplit), an instantiation of its own
+// so that the other launches carry none of its bookkeeping.
+template <int MODE, int NB, int NV, bool AR, bool KS = false>
 __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_constant__ GemvArgs a)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -792,12 +805,20 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     __shared__ __align__(16) uint32_t sargs[(sizeof(GemvArgs) + 3) / 4];
     if (tid < (int)(sizeof(GemvArgs) / 4)) sargs[tid] = reinterpret_cast<const uint32_t*>(&a)[tid];
     const int G = a.groups, R = a.ring_slots;
-    const int per = a.aligned ? G : 1;                                     // tiles per partition item
-    const int t0 = part_start(blockIdx.x, a.part_q, a.part_r) * per;      // first tile of this CTA
-    const int n = (a.part_q + ((int)blockIdx.x < a.part_r ? 1 : 0)) * per; // tiles of this CTA
+    // Column split inside a cluster of two CTAs (FP16, one vector): the partition items are the
+    // clusters' row blocks; this CTA walks, for each of them, the run of G/2 tiles of its half.
+    static_assert(!KS || (MODE == kF16 && NB == 1 && NV == 1 && !AR), "the column split carries one FP16 vector");
+    constexpr bool ksplit = KS;
+    const int krank = ksplit ? (int)(blockIdx.x & 1u) : 0;               // = %cluster_ctarank (clusters along x)
+    const int pid = ksplit ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;   // partition index: cluster or CTA
+    const int run = ksplit ? (G >> 1) : G;                                 // tiles this CTA walks per row block
+    const int per = a.aligned ? run : 1;                                   // tiles per partition item
+    // first tile of this CTA in memory, and its tiles (for ksplit: in runs of `run`, G apart)
+    const int t0 = part_start(pid, a.part_q, a.part_r) * (a.aligned ? G : 1) + krank * run;
+    const int n = (a.part_q + (pid < a.part_r ? 1 : 0)) * per;
     // first and last row block this CTA holds tiles of (whole row blocks: no division needed)
-    const int rb_first = a.aligned ? part_start(blockIdx.x, a.part_q, a.part_r) : (int)((unsigned)t0 / (unsigned)G);
-    const int rb_last = a.aligned ? rb_first + a.part_q - ((int)blockIdx.x < a.part_r ? 0 : 1)
+    const int rb_first = a.aligned ? part_start(pid, a.part_q, a.part_r) : (int)((unsigned)t0 / (unsigned)G);
+    const int rb_last = a.aligned ? rb_first + a.part_q - (pid < a.part_r ? 0 : 1)
                                   : (int)((unsigned)(t0 + n - 1) / (unsigned)G);
 
     uint32_t* xstage = reinterpret_cast<uint32_t*>(smem);              // digits, or the int8 vector
@@ -809,8 +830,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     const uint32_t bar = smem_addr(smem + a.off_bar);
 
     // ---- this warp's tile range, in chunks of four, and the first ring fill ------------
-    const int w0 = t0 + warp_start(warp, n), w1 = t0 + warp_start(warp + 1, n);
-    const int nw = w1 - w0;                                  // may be 0 for tiny problems
+    // v0: this warp's first tile counted along the CTA's walk; w0: the same tile in memory (with
+    // ksplit the walk skips the other CTA's half of every row block)
+    const int v0 = warp_start(warp, n), nw = warp_start(warp + 1, n) - v0;   // nw may be 0 for tiny problems
+    const int vrb = ksplit ? (int)((unsigned)v0 / (unsigned)run) : 0;       // row blocks in front of v0 (ksplit)
+    const int w0 = t0 + v0 + (ksplit ? vrb * (G - run) : 0);
     const int nchunks = (nw + kSlotTiles - 1) / kSlotTiles;
     // this warp's private ring: slots s0 .. s0 + depth - 1 of the CTA's R
     const int depth = (R >> kWarpsLog2) + (warp < (R & (kWarps - 1)) ? 1 : 0);
@@ -834,15 +858,31 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         if ((uint32_t)lane < lines) asm volatile("prefetch.global.L2 [%0];" ::"l"(first + (uintptr_t)lane * 128) : "memory");
     };
     const int cinit = min(depth, nchunks);                   // chunks of the first ring fill
-    for (int c = 0; c < cinit; c++)
-        fill_slot(ring_w + c * kSlotBytes, src_lane + (size_t)c * kSlotBytes, bar_w + c * 8, lane, pieces(c));
-    if (kL2Ahead > 0 && a.l2_prefetch)
+    // the request stream: next chunk's address, and (ksplit) how many tiles of the current run are
+    // still to request -- at its end the stream jumps over the other CTA's half.  Chunks never
+    // straddle a run: runs and warp ranges are multiples of the chunk (the launch plan sees to it).
+    const uint8_t* src_next = src_lane;
+    int run_left = ksplit ? run - (v0 - vrb * run) : 0x7fffffff;
+    auto advance = [&]() {
+        src_next += kSlotBytes;
+        if (ksplit) {
+            run_left -= kSlotTiles;
+            if (run_left <= 0) {
+                src_next += (size_t)(G - run) * kTileBytes;
+                run_left = run;
+            }
+        }
+    };
+    for (int c = 0; c < cinit; c++) {
+        fill_slot(ring_w + c * kSlotBytes, src_next, bar_w + c * 8, lane, pieces(c));
+        advance();
+    }
+    if (kL2Ahead > 0 && a.l2_prefetch && !ksplit)
         for (int c = cinit; c < min(nchunks, cinit + kL2Ahead); c++) l2_chunk(c);
-    const uint8_t* src_next = src_lane + (size_t)cinit * kSlotBytes;      // the next chunk to request
     __syncwarp();
     // paired launch: the partner's shared memory may be written once both CTAs are running
     const bool paired = !I8 && !AR && a.pair;
-    if (paired) cluster_barrier();
+    if (paired || ksplit) cluster_barrier();
     TL(1);
 
     // ---- everything below may depend on the previous kernel in the stream -------
@@ -863,15 +903,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     } else if (I8) {
         stage_x_i8(reinterpret_cast<const int8_t*>(a.x), a.cols, xstage, sx, tid);
     } else {
-        const int g0 = a.x_local ? (int)((unsigned)t0 % (unsigned)G) : 0;
+        const int g0 = ksplit ? krank * run : (a.x_local ? (int)((unsigned)t0 % (unsigned)G) : 0);
+        const int gstage = ksplit ? run : (a.x_local ? n : G);
         const int part = paired ? (int)cluster_rank() : 0, nparts = paired ? 2 : 1;
         const uint32_t peer = paired ? peer_addr(smem_addr(xstage), (uint32_t)(part ^ 1)) : 0u;
         if constexpr (W16)
             stage_x_f16w<NB>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
-                             a.x_local ? n : G, part, nparts, peer);
+                             gstage, part, nparts, peer);
         else
             stage_x_f16<NB, NV>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
-                                a.x_local ? n : G, part, nparts, peer);
+                                gstage, part, nparts, peer);
     }
     // both halves of a paired launch are in place (and no store to the partner is outstanding)
     // once every thread of the two CTAs has passed this barrier; it orders the CTA's own
@@ -901,9 +942,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     const bool xloc = !I8 && a.x_local;
 
     // ---- main loop: this warp's tiles, four per ring slot ----------------------------
-    const int rb0 = (int)((unsigned)w0 / (unsigned)G);
-    int g = w0 - rb0 * G;                    // group (tile inside the row block) of the next tile
-    int gxi = xloc ? (w0 - t0) : g;          // where that group's activations were staged
+    // g: position of the next tile inside this CTA's run of its row block (the group, or with
+    // ksplit the group counted from the CTA's first); a run ends at `run`
+    const int rb0 = ksplit ? rb_first + vrb : (int)((unsigned)w0 / (unsigned)G);
+    int g = ksplit ? v0 - vrb * run : w0 - rb0 * G;
+    int gxi = xloc ? v0 : g;                 // where that group's activations were staged
     int rbr = rb0 - rb_first;                // row block, relative to the CTA's first
     float acc[NB][2];                        // [block][row half h]: rows gq + 8h of the row block
 #pragma unroll
@@ -996,13 +1039,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         ok = mbar_wait(bar_w + kbar, ph);
         if (!ok) break;
         const uint32_t chunk = ring_w - (uint32_t)lane * 16u + koff;
-        if (rem >= kSlotTiles && g + kSlotTiles <= G) {
+        if (rem >= kSlotTiles && g + kSlotTiles <= run) {
             // common case: a whole chunk inside one row block, straight-line code
 #pragma unroll
             for (int q = 0; q < kSlotTiles; q++) tile(chunk + q * kTileBytes, gxi + q);
             g += kSlotTiles;
             gxi += kSlotTiles;
-            if (g == G) {
+            if (g == run) {
                 flush();
                 g = 0;
                 if (!xloc) gxi = 0;
@@ -1014,7 +1057,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
             for (int q = 0; q < nt; q++) {
                 tile(chunk + q * kTileBytes, gxi);
                 gxi++;
-                if (++g == G) {              // row block finished (for this warp)
+                if (++g == run) {            // row block finished (for this warp)
                     flush();
                     g = 0;
                     if (!xloc) gxi = 0;
@@ -1023,7 +1066,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
             }
         }
         rem -= kSlotTiles;
-        if (kL2Ahead > 0 && a.l2_prefetch) {
+        if (kL2Ahead > 0 && a.l2_prefetch && !ksplit) {
             const int cnext = (nw - req + kSlotTiles - 1) / kSlotTiles + kL2Ahead;
             if (cnext < nchunks) l2_chunk(cnext);
         }
@@ -1031,7 +1074,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         __syncwarp();
         if (req > 0) {
             fill_slot(ring_w + koff, src_next, bar_w + kbar, lane, min(kSlotTiles, req) * (kTileBytes / 16));
-            src_next += kSlotBytes;
+            advance();
             req -= kSlotTiles;
         }
         koff += kSlotBytes;
@@ -1140,6 +1183,40 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
             for (int i = 0; i < 5; i++) rec[i] = ts[i];
             rec[5] = epoch;
         }
+        return;
+    }
+
+    if (ksplit) {
+        // ---- the two halves of every row block meet in the first CTA's shared memory: both
+        // CTAs put their row-block sums (warp order) into its exchange buffer -- the second CTA
+        // through the cluster's shared-memory window --, the cluster barrier orders the stores,
+        // and the first CTA adds first half + second half and writes the outputs.
+        float* pb = reinterpret_cast<float*>(smem + e.off_pairbuf);
+        const int nrb_cta = rb_last - rb_first + 1;
+        const uint32_t pb_remote = krank ? peer_addr(smem_addr(pb), 0u) : 0u;
+        for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
+            if (lane < kTileRows) {
+                float v = 0.f;
+                for (uint32_t mk = contrib[r_b - rb_first]; mk; mk &= mk - 1u)     // ascending warp order
+                    v += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + lane];
+                const int slot = (krank * nrb_cta + (r_b - rb_first)) * kTileRows + lane;
+                if (krank)
+                    st_peer(pb_remote + (uint32_t)slot * 4u, __float_as_uint(v));
+                else
+                    pb[slot] = v;
+            }
+        }
+        cluster_barrier();
+        if (krank == 0) {
+            for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
+                const int r = r_b * kTileRows + lane;
+                if (lane < kTileRows && r < e.rows) {
+                    const int slot = (r_b - rb_first) * kTileRows + lane;
+                    *out_ptr(e, 0, r) = __float2half_rn((pb[slot] + pb[nrb_cta * kTileRows + slot]) * oscale);
+                }
+            }
+        }
+        TL(6);
         return;
     }
 
@@ -1381,7 +1458,7 @@ int packed_row_align() { return kTileRows; }
 // columns stored per group (NB * NV * 3 digit columns), force_aligned: whole row blocks per
 // CTA or fail (the fused all-reduce needs it).
 static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool force_aligned, int* grid_out,
-                     size_t* smem_out)
+                     size_t* smem_out, bool allow_clusters = false)
 {
     const int rows = a.rows, cols = a.cols;
     a.groups = cols / kGroup;
@@ -1398,16 +1475,22 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     // Shared-memory layout for one way of cutting the matrix: activations | group constants |
     // partial sums | contributor masks | (fused staging) | mbarriers | ring.  Returns the bytes in
     // front of the ring.
+    // aligned == 2: whole row blocks per CLUSTER of two CTAs, each CTA one half of the columns
     auto layout = [&](int aligned, int* grid, int* n_max_out) {
-        a.aligned = aligned;
+        const bool ks = (aligned == 2);
+        a.aligned = aligned ? 1 : 0;
+        a.ksplit = ks ? 1 : 0;
         const int items = aligned ? nrb : tiles;
-        *grid = items < grid_max ? items : grid_max;
-        a.part_q = items / *grid;
-        a.part_r = items % *grid;
-        const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * (aligned ? a.groups : 1);    // tiles of the largest CTA
+        const int parts_max = ks ? grid_max / 2 : grid_max;
+        const int parts = items < parts_max ? items : parts_max;
+        *grid = ks ? 2 * parts : parts;
+        a.part_q = items / parts;
+        a.part_r = items % parts;
+        const int per = aligned ? (ks ? a.groups / 2 : a.groups) : 1;
+        const int n_max = (a.part_q + (a.part_r ? 1 : 0)) * per;    // tiles of the largest CTA
         *n_max_out = n_max;
-        a.x_local = (!i8 && n_max < a.groups) ? 1 : 0;
-        const int gstaged = a.x_local ? n_max : a.groups;
+        a.x_local = (!i8 && !ks && n_max < a.groups) ? 1 : 0;
+        const int gstaged = ks ? a.groups / 2 : (a.x_local ? n_max : a.groups);
         // staged activations: INT8 two digit columns; FP16 512 bytes per group and vector on 24
         // bits, 1 KB per group for the four vectors of the wide mode
         size_t off = i8 ? (size_t)cols * 2 : (mode == kF16W ? (size_t)gstaged * 1024 : (size_t)gstaged * nvt * 512);
@@ -1420,6 +1503,11 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
         off += (size_t)(max_rb_per_cta + kWarps) * kTileRows * nvt * sizeof(float);
         a.off_mask = (int)off;
         off += (size_t)(max_rb_per_cta + 1) * sizeof(uint32_t);
+        if (ks) {
+            off = (off + 15) & ~(size_t)15;
+            a.off_pairbuf = (int)off;
+            off += (size_t)2 * max_rb_per_cta * kTileRows * sizeof(float);
+        }
         if (fusedx) {
             off = (off + 15) & ~(size_t)15;
             a.off_xtmp = (int)off;
@@ -1448,6 +1536,17 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     if (!aligned && chunks_of(n_max) <= kMaxSlots && off + (size_t)chunks_of(n_max) * kSlotBytes <= kCoResidentBytes)
         aligned = true;
     if (!aligned) off = layout(0, &grid, &n_max);
+    // Long rows, one FP16 vector: the staged activations (4 bytes per column) crowd out the ring
+    // and every CTA converts the whole vector.  Clusters of two CTAs then share whole row
+    // blocks and each CTA takes one half of the columns: half the staging time and footprint, a
+    // deeper ring, and the halves' sums meet in the first CTA's shared memory.  Needs runs of
+    // whole chunks (groups a multiple of 8) and at least 8 tiles per warp in every CTA, so that
+    // warp ranges start on chunk boundaries and no chunk straddles a run.
+    if (TLLM_GEMV_KSPLIT && allow_clusters && aligned && !force_aligned && mode == kF16 && nvt == 1 && a.batch == 1 &&
+        cols >= TLLM_GEMV_KSPLIT_MIN_COLS && (a.groups % (2 * kSlotTiles)) == 0 && grid_max >= 2) {
+        const int parts = nrb < grid_max / 2 ? nrb : grid_max / 2;
+        if ((nrb / parts) * (a.groups / 2) >= 8 * kWarps) off = layout(2, &grid, &n_max);
+    }
     a.late_release = release_rule(rows, cols);
     // Ring: what a CTA can use, bounded by what lets two CTAs share the SM (the launch that
     // follows prefetches its weights beside this one); a problem whose activations leave less
@@ -1466,7 +1565,7 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     // 4096x14336 16.4 -> 13.7 us).  One vector of a long row gains nothing: 4096x14336 9.4 us
     // either way, the stores into the partner's shared memory and the two cluster barriers cost
     // what the halved conversion saves.
-    a.pair = (TLLM_GEMV_PAIR_STAGING && !i8 && !a.x_local && (grid % 2) == 0 && a.batch >= 3 &&
+    a.pair = (TLLM_GEMV_PAIR_STAGING && allow_clusters && !i8 && !a.ksplit && !a.x_local && (grid % 2) == 0 && a.batch >= 3 &&
               (long long)a.groups * 16 * a.batch >= 2 * kThreads) ? 1 : 0;
     // only where the ring is shallow (fewer than two slots per warp): a deeper ring hides the HBM
     // latency by itself and the prefetch instructions then only cost issue slots
@@ -1477,7 +1576,7 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     return TLLM_OK;
 }
 
-template <int MODE, int NB, int NV, bool AR = false>
+template <int MODE, int NB, int NV, bool AR = false, bool KS = false>
 static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     static bool attr[64] = {};
@@ -1487,9 +1586,9 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     {
         std::lock_guard<std::mutex> lk(mu);
         if (dev >= 0 && dev < 64 && !attr[dev]) {
-            const cudaError_t e1 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR>,
+            const cudaError_t e1 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR, KS>,
                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmemBytes);
-            const cudaError_t e2 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR>,
+            const cudaError_t e2 = cudaFuncSetAttribute(gemv_packed_kernel<MODE, NB, NV, AR, KS>,
                                                         cudaFuncAttributePreferredSharedMemoryCarveout,
                                                         cudaSharedmemCarveoutMaxShared);
             if (e1 != cudaSuccess || e2 != cudaSuccess) {
@@ -1510,14 +1609,14 @@ static int launch_mode(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    if (a.pair) {       // clusters of two CTAs (plan_gemv made the grid even)
+    if (a.pair || a.ksplit) {       // clusters of two CTAs (plan_gemv made the grid even)
         at[1].id = cudaLaunchAttributeClusterDimension;
         at[1].val.clusterDim.x = 2;
         at[1].val.clusterDim.y = 1;
         at[1].val.clusterDim.z = 1;
         cfg.numAttrs = 2;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_packed_kernel<MODE, NB, NV, AR>, a);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_packed_kernel<MODE, NB, NV, AR, KS>, a);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(TLLM_ERR_LAUNCH, "gemv_packed launch: %s", cudaGetErrorString(e));
@@ -1534,6 +1633,7 @@ static int dispatch(const GemvArgs& a, int mode, int grid, size_t smem, cudaStre
 {
     switch (mode) {
         case kF16:
+            if (a.batch <= 1 && a.ksplit) return launch_mode<kF16, 1, 1, false, true>(a, grid, smem, stream);
             if (a.batch <= 1) return launch_mode<kF16, 1, 1>(a, grid, smem, stream);
             return launch_mode<kF16, 1, 2>(a, grid, smem, stream);
         case kF16W: return launch_mode<kF16W, 1, 4>(a, grid, smem, stream);
@@ -1595,7 +1695,8 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     int grid = 0;
     size_t smem = 0;
     mode = f16_mode(mode, batch);
-    if ((st = plan_gemv(a, s->sms, mode, (mode == kF16 || mode == kF16W) ? f16_nvt(batch) : 1, kMaxCtas, false, &grid, &smem)))
+    if ((st = plan_gemv(a, s->sms, mode, (mode == kF16 || mode == kF16W) ? f16_nvt(batch) : 1, kMaxCtas, false, &grid, &smem,
+                        true)))
         return st;
     unsigned ticket;
     {
@@ -1774,7 +1875,6 @@ int launch_gemv_packed_noalloc(const uint8_t* packed, const half* x, half* y, in
     int grid = 0;
     size_t smem = 0;
     if ((st = plan_gemv(a, nd->sms, kF16, 1, kNoAllocMaxCtas, false, &grid, &smem))) return st;
-    a.pair = 0;                         // this entry point keeps to plain launches
     a.ws = reinterpret_cast<uint2*>(nd->base);
     a.err = reinterpret_cast<int*>(nd->base + kNoAllocWsBytes);
     a.ws_stride = 2 * kTileRows;
@@ -1843,7 +1943,6 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
     int grid = 0;
     size_t smem = 0;
     if ((st = plan_gemv(a, s->sms, kF16, 1, kMaxCtas, true, &grid, &smem))) return st;
-    a.pair = 0;                         // the all-reduce instantiation stages on its own
     a.ws = s->ws;                       // unused in the aligned split
     a.err = s->misc + 1;
     a.ws_stride = 2 * kRecFloats;
