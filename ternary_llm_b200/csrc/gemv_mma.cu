@@ -807,7 +807,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     const int G = a.groups, R = a.ring_slots;
     // Column split inside a cluster of two CTAs (FP16, one vector): the partition items are the
     // clusters' row blocks; this CTA walks, for each of them, the run of G/2 tiles of its half.
-    static_assert(!KS || (MODE == kF16 && NB == 1 && NV == 1 && !AR), "the column split carries one FP16 vector");
+    static_assert(!KS || (MODE == kF16 && NB == 1 && NV == 1), "the column split carries one FP16 vector");
     constexpr bool ksplit = KS;
     const int krank = ksplit ? (int)(blockIdx.x & 1u) : 0;               // = %cluster_ctarank (clusters along x)
     const int pid = ksplit ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;   // partition index: cluster or CTA
@@ -1114,11 +1114,40 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         const unsigned epoch = ar_epoch_prev + 1u;
         const unsigned epar = epoch & 1u;
         const size_t wslot = (size_t)(epar * e.ar_world + e.ar_rank) * e.ar_rows_max;
+        float* pb = reinterpret_cast<float*>(smem + e.off_pairbuf);
+        const int nrb_cta = rb_last - rb_first + 1;
+        if (ksplit) {
+            // column split: the two halves of every row block meet in the first CTA's shared
+            // memory first (see below); that CTA then takes part in the exchange between ranks
+            const uint32_t pb_remote = krank ? peer_addr(smem_addr(pb), 0u) : 0u;
+            for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
+                if (lane < kTileRows) {
+                    float v = 0.f;
+                    for (uint32_t mk = contrib[r_b - rb_first]; mk; mk &= mk - 1u)
+                        v += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + lane];
+                    const int slot = (krank * nrb_cta + (r_b - rb_first)) * kTileRows + lane;
+                    if (krank)
+                        st_peer(pb_remote + (uint32_t)slot * 4u, __float_as_uint(v));
+                    else
+                        pb[slot] = v;
+                }
+            }
+            cluster_barrier();
+            if (krank) {
+                if (tid == 0) e.ar_epoch[blockIdx.x] = epoch;      // this CTA's launch counter keeps in step
+                return;
+            }
+        }
         for (int r_b = rb_first + warp; r_b <= rb_last; r_b += kWarps) {
             for (int idx = lane; idx < kTileRows; idx += 32) {
                 float s = 0.f;
-                for (uint32_t mk = contrib[r_b - rb_first]; mk; mk &= mk - 1u)          // ascending warp order
-                    s += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + idx];
+                if (ksplit) {
+                    const int slot = (r_b - rb_first) * kTileRows + idx;
+                    s = pb[slot] + pb[nrb_cta * kTileRows + slot];
+                } else {
+                    for (uint32_t mk = contrib[r_b - rb_first]; mk; mk &= mk - 1u)      // ascending warp order
+                        s += part[(size_t)((r_b - rb_first) + (__ffs(mk) - 1)) * kRec + idx];
+                }
                 const int r = r_b * kTileRows + idx;
                 if (r < e.rows) {
                     const uint2 word = make_uint2(__float_as_uint(s), epoch);
@@ -1542,7 +1571,7 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
     // deeper ring, and the halves' sums meet in the first CTA's shared memory.  Needs runs of
     // whole chunks (groups a multiple of 8) and at least 8 tiles per warp in every CTA, so that
     // warp ranges start on chunk boundaries and no chunk straddles a run.
-    if (TLLM_GEMV_KSPLIT && allow_clusters && aligned && !force_aligned && mode == kF16 && nvt == 1 && a.batch == 1 &&
+    if (TLLM_GEMV_KSPLIT && allow_clusters && aligned && mode == kF16 && nvt == 1 && a.batch == 1 &&
         cols >= TLLM_GEMV_KSPLIT_MIN_COLS && (a.groups % (2 * kSlotTiles)) == 0 && grid_max >= 2) {
         const int parts = nrb < grid_max / 2 ? nrb : grid_max / 2;
         if ((nrb / parts) * (a.groups / 2) >= 8 * kWarps) off = layout(2, &grid, &n_max);
@@ -1942,7 +1971,7 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
     a.batch = 1;
     int grid = 0;
     size_t smem = 0;
-    if ((st = plan_gemv(a, s->sms, kF16, 1, kMaxCtas, true, &grid, &smem))) return st;
+    if ((st = plan_gemv(a, s->sms, kF16, 1, kMaxCtas, true, &grid, &smem, true))) return st;
     a.ws = s->ws;                       // unused in the aligned split
     a.err = s->misc + 1;
     a.ws_stride = 2 * kRecFloats;
@@ -1960,6 +1989,7 @@ int launch_gemv_packed_allreduce(const uint8_t* packed, const half* x, half* y, 
             a.ar_trace_cap = g_ar_trace[dev].cap;
         }
     }
+    if (a.ksplit) return launch_mode<kF16, 1, 1, true, true>(a, grid, smem, stream);
     return launch_mode<kF16, 1, 1, true>(a, grid, smem, stream);
 }
 

@@ -65,6 +65,33 @@ def main():
     if rank == 0:
         print("TP_ALLREDUCE_OK" if int(flag.item()) == 1 else "TP_ALLREDUCE_FAIL", flush=True)
 
+    # long rows: the launch runs as clusters of two CTAs that split this rank's columns, and the
+    # first CTA of each cluster takes part in the exchange between the ranks
+    n2, k2 = 4096, 14336 * world
+    nz2, sg2, sc2, x2 = oracle.make_case(n2, k2, seed=78)
+    c0, c1 = rank * k2 // world, (rank + 1) * k2 // world
+    w2 = tl.PreparedWeight(d(np.ascontiguousarray(nz2[:, c0 // 32:c1 // 32])), d(np.ascontiguousarray(sg2[:, c0 // 32:c1 // 32])),
+                           d(np.ascontiguousarray(sc2[:, c0 // 128:c1 // 128])), n2, c1 - c0, register=False)
+    xs2 = d(np.ascontiguousarray(x2[0, c0:c1]))
+    outs2 = []
+    for rep in range(3):
+        y = torch.full((n2,), float("nan"), dtype=torch.float16, device=dev)
+        tl.ternary_gemv_packed_allreduce(w2, xs2, y, ar)
+        outs2.append(y)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    rows2 = np.unique(np.concatenate([np.arange(64), np.arange(n2 - 64, n2), np.random.default_rng(3).integers(0, n2, 256)]))
+    y64b = oracle.ternary_matvec(nz2[rows2], sg2[rows2], sc2[rows2], x2[0], 128, np.float64)
+    boundb = oracle.tolerance_bound(nz2[rows2], sg2[rows2], sc2[rows2], x2[0])
+    half_ulp_b = 0.5 * 2.0 ** (np.floor(np.log2(np.maximum(np.abs(y64b), 2.0 ** -14))) - 10)
+    ok3 = all(bool(torch.equal(y, outs2[0])) for y in outs2)
+    ok3 = ok3 and bool((np.abs(outs2[0].cpu().numpy().astype(np.float64)[rows2] - y64b) <= boundb + half_ulp_b).all())
+    flag3 = torch.tensor([1 if ok3 else 0], device=dev)
+    dist.all_reduce(flag3, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_ALLREDUCE_LONG_ROWS_OK" if int(flag3.item()) == 1 else "TP_ALLREDUCE_LONG_ROWS_FAIL", flush=True)
+    flag = torch.minimum(flag, flag3)
+
     # the whole layer stack, heads and intermediate rows split over the ranks, fused exchange:
     # logits from the replicated residual stream against the unsharded layer oracle
     from oracle import layer_oracle as LO

@@ -204,3 +204,39 @@ def test_three_and_four_vectors_per_pass_keep_the_benchmark_bound_on_outliers():
         err = np.abs(got - y64)
         assert (err <= literal).all(), f"batch {batch}: beyond 2e-3 * sum|scale * x| by {np.max(err / literal):.3g}"
         assert (err[1:] <= tight[1:] + _half_ulp(y64[1:])).all(), "ordinary vectors beside the outlier"
+
+
+@pytest.mark.parametrize("n,k", [(3560, 14336), (2384, 28672), (4096, 12288)])
+def test_column_split_launches_with_ragged_row_counts(n, k):
+    """Long rows run as clusters of two CTAs that split the columns (each stages one half of
+    the activations, the halves' sums meet in shared memory).  Row counts that leave a partial
+    last row block and an uneven number of row blocks per cluster, against the oracle; a second
+    call must give the same bits (the exchange buffers carry nothing over)."""
+    nz, sg, sc, w = _weights(n, k, seed=4000 + n)
+    x = np.random.default_rng(n).standard_normal((1, k)).astype(np.float16)
+    dx = torch.from_numpy(x).to(DEV)
+    y = torch.full((1, n), float("nan"), dtype=torch.float16, device=DEV)
+    y2 = torch.full((1, n), float("nan"), dtype=torch.float16, device=DEV)
+    tl.ternary_gemv_packed(w, dx, y, 1)
+    tl.ternary_gemv_packed(w, dx, y2, 1)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    assert torch.equal(y, y2)
+    _check_rows(y.cpu().numpy(), nz, sg, sc, _sample_rows(n, seed=k), x, f"column split {n}x{k}")
+
+
+def test_column_split_with_matrices_packed_back_to_back():
+    """Two matrices that share a long input vector, streamed as one launch (the fused gate|up
+    form) through the column-split path: every row lands in its own output."""
+    k, ns = 14336, (2048, 2064)
+    torch.cuda.set_device(0)
+    src = [synth.random_ternary_weight(n, k, seed=5000 + i, device=torch.device(DEV)) + (n, k) for i, n in enumerate(ns)]
+    ws = tl.prepare_group(src, keep_source=True)
+    x = np.random.default_rng(5).standard_normal((1, k)).astype(np.float16)
+    dx = torch.from_numpy(x).to(DEV)
+    ys = [torch.full((n,), float("nan"), dtype=torch.float16, device=DEV) for n in ns]
+    tl.ternary_gemv_packed_multi(ws, dx[0], ys)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    for (nz, sg, sc, n, _), y in zip(src, ys):
+        _check_rows(y.cpu().numpy()[None, :], nz, sg, sc, _sample_rows(n, seed=n), x, f"grouped column split, {n} rows")

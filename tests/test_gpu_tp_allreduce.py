@@ -17,4 +17,4 @@ def test_fused_allreduce_two_ranks():
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                         "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "_tp_worker.py")],
                        capture_output=True, text=True, timeout=280, env=env)
-    assert r.returncode == 0 and "TP_ALLREDUCE_OK" in r.stdout and "TP_STACK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and "TP_ALLREDUCE_OK" in r.stdout and "TP_ALLREDUCE_LONG_ROWS_OK" in r.stdout and "TP_STACK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
