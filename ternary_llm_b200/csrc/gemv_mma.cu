@@ -82,7 +82,11 @@ constexpr int kMaxPeers = TLLM_MAX_PEERS;
 #endif
 constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
 // A ring that two co-resident CTAs allow but that holds fewer slots than this (and less than the
-// CTA's whole share) is given up for one CTA per SM with all of the shared memory.
+// CTA's whole share) is given up for one CTA per SM with all of the shared memory.  Measured,
+// the step from co-resident to alone costs far more than a shallow ring does (the launches either
+// side lose their overlap: 8B sweep 0.87 -> 1.02 ms with the limit at 32; the 8192 x 28672 launch
+// of the 70B stack 17 -> 38 us when its ring fell from 24 to 23 slots with the limit at 24), so
+// the limit is the minimum of one slot per warp.
 #ifndef TLLM_GEMV_PAIR_STAGING
 #define TLLM_GEMV_PAIR_STAGING 1
 #endif
@@ -93,7 +97,7 @@ constexpr size_t kCoResidentBytes = TLLM_GEMV_CORESIDENT_BYTES;
 #define TLLM_GEMV_KSPLIT_MIN_COLS 12288
 #endif
 #ifndef TLLM_GEMV_MIN_SHARED_SLOTS
-#define TLLM_GEMV_MIN_SHARED_SLOTS 24
+#define TLLM_GEMV_MIN_SHARED_SLOTS 16
 #endif
 constexpr int kMinSharedSlots = TLLM_GEMV_MIN_SHARED_SLOTS;
 constexpr size_t kMaxSmemBytes = 226 * 1024;      // dynamic part; the kernel also has a few static bytes
