@@ -342,7 +342,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
         launch_step()
         torch.cuda.synchronize()
         tl.check_device_errors()
-        assert bool(torch.isfinite(stack.res).all()), "non-finite residual stream"
+        assert bool(torch.isfinite(stack.out).all()), "non-finite residual stream"
         # parity of the exchange, outside every timed region: layer 0's o and down through the
         # same row-parallel path, rank 0 compares sampled rows with the CPU oracle on the
         # gathered shards (sum over ranks of W_r x_r)
@@ -411,7 +411,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
         def step_e2e():
             x_h.copy_(x_host, non_blocking=True)
             step()
-            y_host.copy_(stack.res, non_blocking=True)
+            y_host.copy_(stack.out, non_blocking=True)
         for _ in range(2):
             step_e2e()
         ms_e2e = timed(step_e2e, args.steps)
@@ -447,7 +447,7 @@ def run_tp(args, torch, dist, tl, synth, rank, world, local, dev):
             s32.step(x32, KV_LEN - 1)
             torch.cuda.synchronize()
             tl.check_device_errors()
-            finite = bool(torch.isfinite(s32.res).all())
+            finite = bool(torch.isfinite(s32.out).all())
             g32, mode32 = capture(lambda: s32.step(x32, KV_LEN - 1))
             fn32 = g32.replay if g32 is not None else (lambda: s32.step(x32, KV_LEN - 1))
             fn32()

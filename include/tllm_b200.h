@@ -183,6 +183,17 @@ int tllm_b200_gemv_int8_packed(const void* packed, const int8_t* input_int8, flo
 int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* const* y, const int* rows,
                                 int cols, const void* x, void* stream);
 
+/* The same with the shared input vector made inside the kernel: x = rmsnorm(a (+ b)) *
+ * norm_weight with the arithmetic of add_forward followed by rmsnorm_forward
+ * (include/kernels.cuh:45-48,64-66: FP16-rounded sum, FP32 mean of squares of the rounded
+ * values, one FP16 rounding), what the reference does with a residual add and an rmsnorm
+ * launch in front of its q/k/v and gate/up projections (src/transformer.cpp:199-217,264-278).  b may be NULL (no residual).  res_out (may be NULL)
+ * receives the rounded sum a + b and must not alias a or b.  The matrices must be packed back
+ * to back (count > 1).  a, b, norm_weight, res_out: FP16 [cols], 16-byte aligned. */
+int tllm_b200_gemv_packed_multi_norm(int count, const void* const* packed, void* const* y, const int* rows, int cols,
+                                     const void* a, const void* b, const void* norm_weight, void* res_out, float eps,
+                                     void* stream);
+
 /*
  * Row-parallel GEMV of a tensor-parallel layer (o_proj, down_proj: each rank holds a
  * 128-aligned K range of the matrix and the matching slice of x) with the all-reduce

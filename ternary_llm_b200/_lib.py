@@ -39,6 +39,7 @@ SIGNATURES = {
     "tllm_b200_gemv_packed_allreduce": (_int, [_vp] * 3 + [_int] * 4 + [_vp] * 2 + [_int, _vp]),
     "tllm_b200_allreduce_trace": (_int, [_vp, _int]),
     "tllm_b200_gemv_packed_multi": (_int, [_int, _vp, _vp, _vp, _int, _vp, _vp]),
+    "tllm_b200_gemv_packed_multi_norm": (_int, [_int, _vp, _vp, _vp, _int, _vp, _vp, _vp, _vp, ctypes.c_float, _vp]),
     # include/tllm_b200_layer.h
     "tllm_b200_rmsnorm": (_int, [_vp] * 5 + [_int, _int, ctypes.c_float, _vp]),
     "tllm_b200_rope": (_int, [_vp, _vp] + [_int] * 6 + [ctypes.c_float, _vp]),

@@ -257,6 +257,24 @@ int tllm_b200_gemv_packed_multi(int count, const void* const* packed, void* cons
                                     (const half*)x, (cudaStream_t)stream);
 }
 
+int tllm_b200_gemv_packed_multi_norm(int count, const void* const* packed, void* const* y, const int* rows, int cols,
+                                     const void* a, const void* b, const void* norm_weight, void* res_out, float eps,
+                                     void* stream)
+{
+    if (!packed || !y || !rows || !a || !norm_weight) return fail(TLLM_ERR_NULL, "null pointer");
+    if (count < 1 || count > TLLM_MAX_FUSED) return fail(TLLM_ERR_BATCH, "count %d outside 1..%d", count, TLLM_MAX_FUSED);
+    for (int i = 0; i < count; i++) {
+        const int st = check_packed_call(packed[i], a, y[i], rows[i], cols);
+        if (st) return st;
+    }
+    if (misaligned(a, 16) || (b && misaligned(b, 16)) || misaligned(norm_weight, 16) || (res_out && misaligned(res_out, 16)))
+        return fail(TLLM_ERR_ALIGN, "gemv_packed_multi_norm: a, b, norm_weight and res_out must be 16-byte aligned");
+    if (res_out && (res_out == a || res_out == b))
+        return fail(TLLM_ERR_SHAPE, "gemv_packed_multi_norm: res_out must not alias an input (other CTAs still read it)");
+    return launch_gemv_packed_multi_norm(count, (const uint8_t* const*)packed, (half* const*)y, rows, cols, (const half*)a,
+                                         (const half*)b, (const half*)norm_weight, (half*)res_out, eps, (cudaStream_t)stream);
+}
+
 int tllm_b200_gemv_packed_allreduce(const void* packed, const void* x, void* y, int rows, int cols, int rank, int world,
                                     void* const* peer_recv, void* epoch_local, int rows_max, void* stream)
 {

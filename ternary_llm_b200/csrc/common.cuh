@@ -60,6 +60,9 @@ int launch_gemv_int8_packed_multi(int count, const uint8_t* const* packed, half*
 //   norm: x = quantise(rmsnorm(a (+ b)) * w), half(a + b) stored to res_out (may be null)
 //   silu: x = quantise(silu(gate) * up)
 //   quant: x = quantise(x_f16)
+int launch_gemv_packed_multi_norm(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
+                                  const half* a, const half* b, const half* w, half* res_out, float eps,
+                                  cudaStream_t stream);
 int launch_gemv_int8_packed_norm(const uint8_t* packed, const half* a, const half* b, const half* w, half* res_out,
                                  float eps, half* y, int rows, int cols, cudaStream_t stream);
 int launch_gemv_int8_packed_silu(const uint8_t* packed, const half* gate, const half* up, half* y, int rows, int cols,

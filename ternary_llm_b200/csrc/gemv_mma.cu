@@ -118,7 +118,9 @@ constexpr int kL2Ahead = TLLM_GEMV_L2_AHEAD_CHUNKS;
 // produced inside the kernel's staging phase from FP16 inputs (stage_x_fused below).
 // kF16W: FP16 activations, four vectors per MMA column block on 16-bit block fixed point (two
 // 8-bit digits per vector) instead of two vectors on 24 bits: batches of three and more.
-enum Mode { kF16 = 0, kF16W = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4, kI8Quant = 5 };
+// kF16Norm: FP16 arithmetic like kF16 (one vector), the vector is rmsnorm(fx_a (+ fx_b)) * fx_w made in
+// the staging phase (the FP16-rounded sum goes to fx_res_out), as kI8Norm does for the INT8 path.
+enum Mode { kF16 = 0, kF16W = 1, kI8 = 2, kI8Norm = 3, kI8Silu = 4, kI8Quant = 5, kF16Norm = 6 };
 
 struct GemvArgs {
     const uint8_t* packed;
@@ -384,7 +386,8 @@ __device__ __forceinline__ void quad_digits(uint32_t u0, uint32_t u1, uint32_t u
 // part / nparts / peer: with nparts == 2 this CTA converts every second batch of kThreads items
 // (those of parity `part`) and stores each result word to its own shared memory and, at `peer`
 // (the partner's address of xdig; the constants follow at the same distance), to the partner's.
-template <int NB, int NV>
+// SMEM_SRC: x is a vector in shared memory (made by norm_to_smem), read with plain loads.
+template <int NB, int NV, bool SMEM_SRC = false>
 __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols, int groups, int batch,
                                             uint32_t* xdig, uint4* xcst, int tid, int g0, int gcount,
                                             int part = 0, int nparts = 1, uint32_t peer = 0)
@@ -410,7 +413,9 @@ __device__ __forceinline__ void stage_x_f16(const half* __restrict__ x, int cols
         const int el = item - b * per_vec;
         int gg = g0 + (el >> 4);
         if (gg >= groups) gg -= groups;
-        return __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16);
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)b * cols) + (gg << 4) + l16;
+        if (SMEM_SRC) return *src;
+        return __ldg(src);
     };
     const int stride = kThreads * nparts;
     int item = tid + part * kThreads;
@@ -677,6 +682,48 @@ __device__ __forceinline__ void stage_x_i8(const int8_t* __restrict__ x, int col
 //   kI8Silu  "SwiGLU, absmax quantise" (src/transformer.cpp:284-288): o = half(silu(a) * b), then as above.
 //   kI8Quant the quantiser alone (src/transformer.cpp:126-136): o = a.
 // Returns the activation scale.  tmp: half [cols]; red: 33 floats; sx: int [groups].
+// tmp[cols] (shared memory) = FP16(rmsnorm(a (+ b)) * w), the arithmetic of the stand-alone
+// rmsnorm operator: FP16-rounded sum first (stored to res_out by CTA 0 when a and b are both
+// given), mean of squares and scaling in FP32, one FP16 rounding of the result.  Every CTA of
+// the GEMV computes the whole vector (the inputs are a few KB in L2).  Ends with a barrier.
+__device__ __forceinline__ void norm_to_smem(const GemvArgs& a, half* tmp, float* red, int tid)
+{
+    const int n8 = a.cols >> 3;
+    float ss = 0.f;
+    for (int i = tid; i < n8; i += kThreads) {
+        const uint4 ar = *(reinterpret_cast<const uint4*>(a.fx_a) + i);
+        uint4 st4 = ar;
+        if (a.fx_b) {
+            const uint4 br = *(reinterpret_cast<const uint4*>(a.fx_b) + i);
+            const half* ah = reinterpret_cast<const half*>(&ar);
+            const half* bh = reinterpret_cast<const half*>(&br);
+            half* sth = reinterpret_cast<half*>(&st4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) sth[j] = __float2half_rn(__half2float(ah[j]) + __half2float(bh[j]));
+            if (a.fx_res_out && blockIdx.x == 0) *(reinterpret_cast<uint4*>(a.fx_res_out) + i) = st4;
+        }
+        const half* vh = reinterpret_cast<const half*>(&st4);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float v = __half2float(vh[j]);
+            ss += v * v;
+        }
+        *(reinterpret_cast<uint4*>(tmp) + i) = st4;
+    }
+    const float var = cta_sum(ss, red, tid) / (float)a.cols;
+    const float rinv = rsqrtf(var + a.fx_eps);
+    for (int i = tid; i < n8; i += kThreads) {
+        uint4 v4 = *(reinterpret_cast<const uint4*>(tmp) + i);
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(a.fx_w) + i);
+        half* vh = reinterpret_cast<half*>(&v4);
+        const half* wh = reinterpret_cast<const half*>(&w4);
+#pragma unroll
+        for (int j = 0; j < 8; j++) vh[j] = __float2half_rn(__half2float(vh[j]) * rinv * __half2float(wh[j]));
+        *(reinterpret_cast<uint4*>(tmp) + i) = v4;
+    }
+    __syncthreads();
+}
+
 template <int MODE>
 __device__ __forceinline__ float stage_x_fused(const GemvArgs& a, uint32_t* xq, int* sx, half* tmp, float* red, int tid)
 {
@@ -782,6 +829,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
     constexpr bool FUSEDX = (MODE == kI8Norm || MODE == kI8Silu || MODE == kI8Quant);
     constexpr bool I8 = (MODE == kI8 || FUSEDX);
     constexpr bool W16 = (MODE == kF16W);         // four vectors per column block, two 8-bit digits each
+    constexpr bool F16N = (MODE == kF16Norm);     // FP16 digits of a vector normalised in the staging phase
     constexpr int NVT = NB * NV;                  // vectors per weight pass
     static_assert(!I8 || (NB == 1 && NV == 1), "INT8 modes carry one vector");
     static_assert(!W16 || NV == 4, "the wide FP16 mode carries four vectors per column block");
@@ -911,7 +959,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_packed_kernel(const __grid_c
         const int gstage = ksplit ? run : (a.x_local ? n : G);
         const int part = paired ? (int)cluster_rank() : 0, nparts = paired ? 2 : 1;
         const uint32_t peer = paired ? peer_addr(smem_addr(xstage), (uint32_t)(part ^ 1)) : 0u;
-        if constexpr (W16)
+        if constexpr (F16N) {
+            half* tmp = reinterpret_cast<half*>(smem + a.off_xtmp);
+            norm_to_smem(a, tmp, reinterpret_cast<float*>(smem + a.off_xtmp + (size_t)a.cols * sizeof(half)), tid);
+            stage_x_f16<NB, NV, true>(tmp, a.cols, G, 1, xstage, xcst, tid, g0, gstage);
+        } else if constexpr (W16)
             stage_x_f16w<NB>(reinterpret_cast<const half*>(a.x), a.cols, G, a.batch, xstage, xcst, tid, g0,
                              gstage, part, nparts, peer);
         else
@@ -1541,7 +1593,7 @@ static int plan_gemv(GemvArgs& a, int sms, int mode, int nvt, int max_ctas, bool
             a.off_pairbuf = (int)off;
             off += (size_t)2 * max_rb_per_cta * kTileRows * sizeof(float);
         }
-        if (fusedx) {
+        if (fusedx || mode == kF16Norm) {
             off = (off + 15) & ~(size_t)15;
             a.off_xtmp = (int)off;
             off += (size_t)cols * sizeof(half) + 64 * sizeof(float);
@@ -1670,6 +1722,7 @@ static int dispatch(const GemvArgs& a, int mode, int grid, size_t smem, cudaStre
             if (a.batch <= 1) return launch_mode<kF16, 1, 1>(a, grid, smem, stream);
             return launch_mode<kF16, 1, 2>(a, grid, smem, stream);
         case kF16W: return launch_mode<kF16W, 1, 4>(a, grid, smem, stream);
+        case kF16Norm: return launch_mode<kF16Norm, 1, 1>(a, grid, smem, stream);
         case kI8Norm: return launch_mode<kI8Norm, 1, 1>(a, grid, smem, stream);
         case kI8Silu: return launch_mode<kI8Silu, 1, 1>(a, grid, smem, stream);
         case kI8Quant: return launch_mode<kI8Quant, 1, 1>(a, grid, smem, stream);
@@ -1729,7 +1782,7 @@ static int launch_packed_once(const uint8_t* packed, const void* x, half* y, flo
     size_t smem = 0;
     mode = f16_mode(mode, batch);
     if ((st = plan_gemv(a, s->sms, mode, (mode == kF16 || mode == kF16W) ? f16_nvt(batch) : 1, kMaxCtas, false, &grid, &smem,
-                        true)))
+                        mode != kF16Norm)))
         return st;
     unsigned ticket;
     {
@@ -1779,6 +1832,29 @@ int launch_gemv_packed_multi(int count, const uint8_t* const* packed, half* cons
                              const half* x, cudaStream_t stream)
 {
     return gemv_packed_multi_any(count, packed, y, rows, cols, x, nullptr, nullptr, stream);
+}
+
+// FP16 GEMV over 1..4 matrices packed back to back whose shared input vector is made in the
+// kernel's staging phase: x = rmsnorm(a (+ b)) * w, the rounded sum a + b stored to res_out.
+int launch_gemv_packed_multi_norm(int count, const uint8_t* const* packed, half* const* y, const int* rows, int cols,
+                                  const half* a, const half* b, const half* w, half* res_out, float eps,
+                                  cudaStream_t stream)
+{
+    const FusedX fx = {a, b, w, res_out, eps};
+    if (count == 1)
+        return launch_packed_once(packed[0], nullptr, y[0], 1.0f, kF16Norm, 1, rows[0], cols, stream, nullptr, &fx);
+    SegY seg = {};
+    seg.n = count;
+    int total = 0;
+    for (int i = 0; i < count; i++) {
+        if (i + 1 < count && ((rows[i] % kTileRows) != 0 || packed[i + 1] != packed[i] + packed_bytes(rows[i], cols)))
+            return fail(TLLM_ERR_SHAPE, "gemv_packed_multi_norm: the matrices must be packed back to back "
+                        "(row counts multiples of %d but the last)", kTileRows);
+        seg.rows[i] = rows[i];
+        seg.y[i] = y[i];
+        total += rows[i];
+    }
+    return launch_packed_once(packed[0], nullptr, nullptr, 1.0f, kF16Norm, 1, total, cols, stream, nullptr, &fx, &seg);
 }
 
 // The same for INT8 activations whose scale stays in device memory (written by the

@@ -218,6 +218,27 @@ def ternary_gemv_packed_multi(weights, input, outputs) -> None:
                                                       _chk(input, torch.float16, "input", cols), _stream()))
 
 
+def ternary_gemv_packed_multi_norm(weights, a, b, norm_weight, res_out, eps: float, outputs) -> None:
+    """y_i = W_i x with x = rmsnorm(a (+ b)) * norm_weight made inside the launch (b and res_out
+    may be None; res_out receives a + b and must be a different tensor).  weights: matrices
+    packed back to back (prepare_group), or a single prepared matrix in a list."""
+    import ctypes
+    n = len(weights)
+    cols = weights[0].cols
+    if any(w.cols != cols for w in weights) or len(outputs) != n:
+        raise ValueError("fused matrices must share the column count and have one output each")
+    if res_out is not None and (res_out.data_ptr() == a.data_ptr() or (b is not None and res_out.data_ptr() == b.data_ptr())):
+        raise ValueError("res_out must not alias an input")
+    packed = (ctypes.c_void_p * n)(*[_chk(w.packed, torch.uint8, "packed weights") for w in weights])
+    ys = (ctypes.c_void_p * n)(*[_chk(y, torch.float16, "output", w.rows) for w, y in zip(weights, outputs)])
+    rows = (ctypes.c_int * n)(*[w.rows for w in weights])
+    _lib.check(_lib.lib().tllm_b200_gemv_packed_multi_norm(
+        n, packed, ys, rows, cols, _chk(a, torch.float16, "a", cols),
+        _chk(b, torch.float16, "b", cols) if b is not None else None,
+        _chk(norm_weight, torch.float16, "norm_weight", cols),
+        _chk(res_out, torch.float16, "res_out", cols) if res_out is not None else None, float(eps), _stream()))
+
+
 AR_MAX_CTAS = 256
 
 

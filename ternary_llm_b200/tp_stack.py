@@ -102,12 +102,14 @@ class TpLayerStack:
         self.k_cache = z(n, B, self.hkv, cfg.max_seq_len, hd)
         self.v_cache = z(n, B, self.hkv, cfg.max_seq_len, hd)
         self.res, self.h = z(B, cfg.hidden), z(B, cfg.hidden)
+        self.res2 = z(B, cfg.hidden)          # the residual stream alternates between res and res2 at batch 1
         self.q, self.k, self.v = z(B, self.hq * hd), z(B, self.hkv * hd), z(B, self.hkv * hd)
         self.attn, self.yo = z(B, self.hq * hd), z(B, cfg.hidden)
         self.g, self.u = z(B, cfg.intermediate // world), z(B, cfg.intermediate // world)
         self.act, self.yd = z(B, cfg.intermediate // world), z(B, cfg.hidden)
         self.ar = ops.FusedAllReduce(group, cfg.hidden, device) if allreduce == "fused" else None
         self.launches_per_step = 0
+        self.out = self.res                   # what the last step returned
 
     # -- pieces -----------------------------------------------------------------------------
     def _column(self, ws, x, ys):
@@ -141,23 +143,19 @@ class TpLayerStack:
         c, B, hd = self.cfg, self.batch, self.cfg.head_dim
         if pos < 0 or pos >= c.max_seq_len:
             raise ValueError(f"position {pos} outside the cache of {c.max_seq_len}")
+        if B == 1:
+            return self._step_one(x, pos)
         n = 0
         self.res.copy_(x.reshape(B, c.hidden))
         L.rmsnorm_forward(self.res, self.layers[0][4], self.h, None, None, B, c.hidden, c.rms_norm_eps)
         n += 2
         for li, (qkv, o, gu, down, _, ffn_norm) in enumerate(self.layers):
             n += self._column(qkv, self.h, [self.q, self.k, self.v])
-            if B == 1:      # RoPE, cache append and attention in one launch
-                L.attention_decode(self.q, self.k, self.v, self.k_cache[li], self.v_cache[li], self.attn, self.hq,
-                                   self.hkv, hd, pos, c.rope_theta, c.max_seq_len)
-                n += 1
-            else:
-                L.rope_append(self.q, self.k, self.v, self.k_cache[li], self.v_cache[li], B, 1, self.hq, self.hkv, hd,
-                              pos, c.rope_theta, c.max_seq_len)
-                L.attention_forward(self.q, self.k_cache[li], self.v_cache[li], self.attn, B, self.hq, self.hkv, hd,
-                                    1, pos + 1, c.max_seq_len)
-                n += 2
-            n += self._row(o, self.attn, self.yo)
+            L.rope_append(self.q, self.k, self.v, self.k_cache[li], self.v_cache[li], B, 1, self.hq, self.hkv, hd,
+                          pos, c.rope_theta, c.max_seq_len)
+            L.attention_forward(self.q, self.k_cache[li], self.v_cache[li], self.attn, B, self.hq, self.hkv, hd,
+                                1, pos + 1, c.max_seq_len)
+            n += 2 + self._row(o, self.attn, self.yo)
             # res += o-projection; h = norm(res)
             L.rmsnorm_forward(self.yo, ffn_norm, self.h, self.res, self.res, B, c.hidden, c.rms_norm_eps)
             n += 1 + self._column(gu, self.h, [self.g, self.u])
@@ -170,7 +168,40 @@ class TpLayerStack:
                 L.add_forward(self.res, self.yd, self.res, self.res.numel())
             n += 1
         self.launches_per_step = n
+        self.out = self.res
         return self.res
+
+    def _step_one(self, x, pos: int):
+        """Batch 1: six launches per layer.  The residual add and the RMSNorm in front of the
+        column-parallel projections run inside their GEMV launch (ternary_gemv_packed_multi_norm),
+        RoPE + cache append + attention are one launch; the residual stream alternates between
+        two buffers because the fused launch must not overwrite the vector other CTAs still read."""
+        c, hd = self.cfg, self.cfg.head_dim
+        cur, nxt = self.res, self.res2
+        cur.copy_(x.reshape(1, c.hidden))
+        n = 1
+        pending = None                       # the row-parallel result not yet added to the residual stream
+        for li, (qkv, o, gu, down, attn_norm, ffn_norm) in enumerate(self.layers):
+            if pending is None:
+                ops.ternary_gemv_packed_multi_norm(qkv, cur[0], None, attn_norm, None, c.rms_norm_eps,
+                                                   [self.q[0], self.k[0], self.v[0]])
+            else:
+                ops.ternary_gemv_packed_multi_norm(qkv, pending[0], cur[0], attn_norm, nxt[0], c.rms_norm_eps,
+                                                   [self.q[0], self.k[0], self.v[0]])
+                cur, nxt = nxt, cur
+            L.attention_decode(self.q, self.k, self.v, self.k_cache[li], self.v_cache[li], self.attn, self.hq,
+                               self.hkv, hd, pos, c.rope_theta, c.max_seq_len)
+            n += 2 + self._row(o, self.attn, self.yo)
+            ops.ternary_gemv_packed_multi_norm(gu, self.yo[0], cur[0], ffn_norm, nxt[0], c.rms_norm_eps,
+                                               [self.g[0], self.u[0]])
+            cur, nxt = nxt, cur
+            L.silu_mul_forward(self.g, self.u, self.act, self.act.numel())
+            n += 2 + self._row(down, self.act, self.yd)
+            pending = self.yd
+        L.add_forward(cur, self.yd, nxt, cur.numel())
+        self.launches_per_step = n + 1
+        self.out = nxt
+        return nxt
 
     def weight_bytes(self) -> int:
         return sum(w.packed.numel() for (qkv, o, gu, down, _, _) in self.layers for w in (*qkv, o, *gu, down))

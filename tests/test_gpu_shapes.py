@@ -240,3 +240,44 @@ def test_column_split_with_matrices_packed_back_to_back():
     tl.check_device_errors()
     for (nz, sg, sc, n, _), y in zip(src, ys):
         _check_rows(y.cpu().numpy()[None, :], nz, sg, sc, _sample_rows(n, seed=n), x, f"grouped column split, {n} rows")
+
+
+@pytest.mark.parametrize("k,ns,with_residual", [(4096, (4096, 1024, 1024), True), (8192, (3584, 3584), True),
+                                                (2048, (8192,), False), (4096, (512, 528), True)])
+def test_gemv_with_residual_add_and_rmsnorm_staged_in_the_launch(k, ns, with_residual):
+    """ternary_gemv_packed_multi_norm: x = rmsnorm(a + b) * w is made inside the GEMV launch.
+    The rounded sum must come out bit for bit, and the projections must match the oracle
+    applied to the oracle's own add + rmsnorm of the same inputs."""
+    from oracle import layer_oracle as LO
+    torch.cuda.set_device(0)
+    src = [synth.random_ternary_weight(n, k, seed=6000 + i + k, device=torch.device(DEV)) + (n, k) for i, n in enumerate(ns)]
+    ws = tl.prepare_group(src, keep_source=True) if len(ns) > 1 else [tl.PreparedWeight(*src[0], register=False)]
+    rng = np.random.default_rng(k)
+    a = rng.standard_normal(k).astype(np.float16)
+    b = (3.0 * rng.standard_normal(k)).astype(np.float16) if with_residual else None
+    w = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float16)
+    eps = 1e-5
+    s16 = (a.astype(np.float32) + b.astype(np.float32)).astype(np.float16) if with_residual else a
+    h, _ = LO.rmsnorm(s16[None, :], w, eps)
+    da, dw = torch.from_numpy(a).to(DEV), torch.from_numpy(w).to(DEV)
+    db = torch.from_numpy(b).to(DEV) if with_residual else None
+    res = torch.full((k,), float("nan"), dtype=torch.float16, device=DEV) if with_residual else None
+    ys = [torch.full((n,), float("nan"), dtype=torch.float16, device=DEV) for n in ns]
+    tl.ternary_gemv_packed_multi_norm(ws, da, db, dw, res, eps, ys)
+    torch.cuda.synchronize()
+    tl.check_device_errors()
+    if with_residual:
+        assert np.array_equal(res.cpu().numpy().view(np.uint16), s16.view(np.uint16)), "residual sum"
+        with pytest.raises(ValueError):
+            tl.ternary_gemv_packed_multi_norm(ws, da, db, dw, da, eps, ys)
+    # the kernel's rsqrtf and the oracle's 1/sqrt may differ in the last FP16 place of x: compare
+    # through the bound on the oracle's x plus the effect of one ulp of x
+    for (nz, sg, sc, n, _), y in zip(src, ys):
+        rows = _sample_rows(n, seed=n)
+        hnz, hsg, hsc = _host_rows(nz, sg, sc, rows)
+        y64, bound = exact_and_bound(hnz, hsg, hsc, h.astype(np.float16))
+        ulp_x = np.abs(h.astype(np.float64)) * 2.0 ** -10
+        extra = exact_and_bound(hnz, hsg, hsc, ulp_x.astype(np.float16))[1] / 2e-3      # sum |scale * t| * ulp(x)
+        got = y.cpu().numpy().astype(np.float64)[None, rows]
+        assert np.isfinite(got).all()
+        assert (np.abs(got - y64) <= bound + extra + _half_ulp(y64)).all(), f"{n} rows of {ns}, K={k}"
