@@ -281,3 +281,25 @@ def test_gemv_with_residual_add_and_rmsnorm_staged_in_the_launch(k, ns, with_res
         got = y.cpu().numpy().astype(np.float64)[None, rows]
         assert np.isfinite(got).all()
         assert (np.abs(got - y64) <= bound + extra + _half_ulp(y64)).all(), f"{n} rows of {ns}, K={k}"
+
+
+def test_random_shapes_and_batches_against_the_oracle():
+    """Forty seeded (rows, columns, vectors) draws -- odd row counts, one to eight vectors, short
+    and long rows, few and many row blocks -- through tllm_b200_gemv_packed, every output of the
+    small ones and sampled rows of the large ones against the oracle."""
+    rng = np.random.default_rng(2026)
+    draws = []
+    for _ in range(30):
+        draws.append((int(rng.integers(1, 700)), 128 * int(rng.integers(1, 17)), int(rng.integers(1, 9))))
+    for _ in range(10):          # large: many row blocks per CTA, long rows, partial last row block
+        draws.append((int(rng.integers(2400, 9000)), 128 * int(rng.choice([16, 32, 56, 64, 96, 112, 224])),
+                      int(rng.choice([1, 1, 2, 3, 4]))))
+    for n, k, batch in draws:
+        nz, sg, sc, w = _weights(n, k, seed=n * 31 + k)
+        x = rng.standard_normal((batch, k)).astype(np.float16)
+        y = torch.full((batch, n), float("nan"), dtype=torch.float16, device=DEV)
+        tl.ternary_gemv_packed(w, torch.from_numpy(x).to(DEV), y, batch)
+        torch.cuda.synchronize()
+        rows = np.arange(n) if n <= 700 else _sample_rows(n, count=128, seed=k)
+        _check_rows(y.cpu().numpy(), nz, sg, sc, rows, x, f"random draw {n}x{k} batch {batch}")
+    tl.check_device_errors()
