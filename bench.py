@@ -926,7 +926,7 @@ def run_ours(args):
             "config": {"workload": "ternary GEMV sweep, LLaMA-3-8B projection shapes (q,k,v,o,gate,up,down) x 32 layers, batch 1",
                        "gemv_per_step": gemvs_per_step, "kernel_launches_per_step": launches_per_step, "bytes_per_step": STEP_BYTES,
                        "l2": "1.85 GB of distinct weights per step (> 126 MB L2), no flush needed",
-                       "launch": "CUDA graph replay of the whole step; q|k|v and gate|up are packed back to back at load time and each group is streamed as one matrix in one launch (they share the input vector); o and down one launch each",
+                       "launch": "CUDA graph replay of the whole step; q|k|v and gate|up are packed back to back at load time and each group is streamed as one matrix in one launch (they share the input vector); o and down one launch each (down, 14336 columns, as clusters of two CTAs that split the columns)",
                        "parallelism": "independent replicas per GPU" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": ROOF_TRAFFIC, "peak_kind": peak_kind,
@@ -946,7 +946,7 @@ def run_ours(args):
         }
         if batch_rows is not None:
             out["gemv_batch"] = {"note": "one launch per distinct matrix (32), CUDA graph, L2 flushed before every timed replay, median of 5; "
-                                         "batch <= 8 is the streaming GEMV (four vectors per weight pass), batch 16 the tcgen05 kernel",
+                                         "batch <= 8 is the streaming GEMV (one or two vectors on 24-bit block fixed point; three and four vectors per weight pass on 16-bit block fixed point, within the 2e-3 bound for any input), batch 16 the tcgen05 kernel",
                                  "rows": batch_rows}
         if ref_cuda is not None:
             out["reference_cuda"] = ref_cuda
